@@ -1,0 +1,125 @@
+/*
+ * pam_b200 — C ABI of the B200 (sm_100a) kernels for piecewise affine multiplication (PAM).
+ *
+ * This is the drop-in boundary for the native layer of epfml/pam: each entry point replaces one
+ * of the functions the reference binds from pam/cuda_kernels.cu (its pybind table, lines
+ * 932-947), or fuses a chain of them that the reference runs from Python.  Conventions:
+ *
+ *   - every pointer is a DEVICE pointer to fp32 data on the device that is current for the
+ *     calling thread; nothing here allocates, frees or synchronises (scratch is passed in);
+ *   - sizes and strides are int64 element counts; `stream` is a cudaStream_t passed as void*;
+ *   - `offset` is the reference's float offset (1.0f = none); the integer added to the bit
+ *     pattern is bits(offset) - 0x3f800000, exactly as pam/cuda_kernels.cu:168 derives it;
+ *   - the return value is PAMK_OK or a negative PAMK_ERR_* code; on PAMK_ERR_CUDA
+ *     pamk_last_cuda_error() returns the cudaError_t of the failed launch;
+ *   - results follow the reference bit for bit for every per-element operation; sums
+ *     (matrix products, row reductions) add the same terms, matrix products in the same
+ *     k order unless split-K is requested (see pamk_matmul).
+ */
+#ifndef PAM_B200_H
+#define PAM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PAMK_OK 0
+#define PAMK_ERR_ARG (-1)          /* null pointer, negative size, unknown enum value      */
+#define PAMK_ERR_SIZE (-2)         /* a dimension exceeds what the kernel indexes           */
+#define PAMK_ERR_LAYOUT (-3)       /* neither of a matrix's two strides is 1                */
+#define PAMK_ERR_WORKSPACE (-4)    /* scratch buffer missing, misaligned or too small       */
+#define PAMK_ERR_CUDA (-5)         /* a CUDA call failed; see pamk_last_cuda_error()        */
+
+const char* pamk_status_string(int status);
+int pamk_last_cuda_error(void);
+/* ABI version of this header (bumped when a signature changes). */
+int pamk_abi_version(void);
+
+/* ---- operand descriptors for the elementwise entry points ---------------------------------
+ * The reference broadcasts in Python and materialises the expanded operand
+ * (pam/cuda_bindings.py:60-63, pam/cuda_kernels.cu:163-164).  Here the broadcast is described
+ * instead: an operand is (ptr, kind); with `n` output elements viewed as [n / inner, inner],
+ *   PAMK_FULL    ptr[i]              one value per output element
+ *   PAMK_SCALAR  ptr[0]              a 0-d device tensor
+ *   PAMK_ROW     ptr[i % inner]      a vector along the last dimension (e.g. LayerNorm weight)
+ *   PAMK_COL     ptr[i / inner]      one value per row (e.g. a row-wise denominator)
+ *   PAMK_IMM     the float passed beside the pointer (a Python number); ptr is ignored
+ */
+#define PAMK_FULL 0
+#define PAMK_SCALAR 1
+#define PAMK_ROW 2
+#define PAMK_COL 3
+#define PAMK_IMM 4
+
+/* out[i] = pam(a, b)            replaces pam_fwd  — elementwise_pam_caller, cuda_kernels.cu:155-183 */
+int pamk_pam_fwd(const float* a, int a_kind, float a_imm, const float* b, int b_kind, float b_imm,
+                 float* out, int64_t n, int64_t inner, float offset, void* stream);
+/* out[i] = pad(a, b)            replaces pad_fwd  — elementwise_pad_caller, cuda_kernels.cu:251-279 */
+int pamk_pad_fwd(const float* a, int a_kind, float a_imm, const float* b, int b_kind, float b_imm,
+                 float* out, int64_t n, int64_t inner, float offset, void* stream);
+/* out[i] = pam_bwd(a, b, dc): exact d pam(a,b)/da * dc
+ *                               replaces pam_bwd — elementwise_pam_bwd_caller, cuda_kernels.cu:200-232 */
+int pamk_pam_bwd(const float* a, int a_kind, float a_imm, const float* b, int b_kind, float b_imm,
+                 const float* dc, int dc_kind, float dc_imm,
+                 float* out, int64_t n, int64_t inner, float offset, void* stream);
+/* out[i] = pad_bwd(a, b, dc): exact d pad(a,b)/db * dc
+ *                               replaces pad_bwd — elementwise_pad_bwd_caller, cuda_kernels.cu:296-328 */
+int pamk_pad_bwd(const float* a, int a_kind, float a_imm, const float* b, int b_kind, float b_imm,
+                 const float* dc, int dc_kind, float dc_imm,
+                 float* out, int64_t n, int64_t inner, float offset, void* stream);
+/* y = base^x                    replaces pa_exp_fwd — elementwise_pa_exp_caller, cuda_kernels.cu:348-373 */
+int pamk_pa_exp_fwd(const float* x, float* y, int64_t n, float base, float offset, void* stream);
+/* exact backward of base^x      replaces pa_exp_bwd — cuda_kernels.cu:395-423 */
+int pamk_pa_exp_bwd(const float* x, const float* dy, float* dx, int64_t n, float base, float offset,
+                    void* stream);
+/* y = log_base(x)               replaces pa_log_fwd — cuda_kernels.cu:443-468 */
+int pamk_pa_log_fwd(const float* x, float* y, int64_t n, float base, float offset, void* stream);
+/* exact backward of log_base(x) replaces pa_log_bwd — cuda_kernels.cu:488-516 */
+int pamk_pa_log_bwd(const float* x, const float* dy, float* dx, int64_t n, float base, float offset,
+                    void* stream);
+
+/* ---- matrix products ------------------------------------------------------------------------
+ * C[z][i][j] = sum_k MUL(A[z][i][k], B[z][k][j]),  C contiguous [batch, M, N].
+ * Operands are addressed by element strides (batch, row, column); for each operand one of the
+ * two matrix strides must be 1 — the reference's row-/column-major flags
+ * (pam/cuda_bindings.py:106-115) are exactly these two cases.  batch == 1 is the 2-D product.
+ *
+ * Replaces pam_matmul_fwd / pam_bmm_fwd (mul_kind PAMK_MUL_PAM) and standard_matmul /
+ * standard_bmm (PAMK_MUL_STANDARD): matmul_caller, cuda_kernels.cu:648-723.
+ *
+ * split_k: 1  = every output is summed by one thread strictly in k order, as the reference does;
+ *               results are then bit-identical to the reference's.
+ *          >1 = K is cut into that many contiguous ranges summed independently and then added in
+ *               range order (deterministic, but a different association than the reference);
+ *               needs `workspace` of pamk_matmul_workspace_bytes(...) bytes, 256-byte aligned.
+ *          0  = let the library choose; it only splits when `workspace` is large enough.
+ */
+#define PAMK_MUL_PAM 0
+#define PAMK_MUL_STANDARD 1
+int pamk_matmul(int mul_kind, const float* A, const float* B, float* C,
+                int64_t batch, int64_t M, int64_t N, int64_t K,
+                int64_t sAb, int64_t sAm, int64_t sAk,
+                int64_t sBb, int64_t sBk, int64_t sBn,
+                float offset, int split_k, void* workspace, size_t workspace_bytes, void* stream);
+/* Scratch needed by pamk_matmul for a given split_k (0 for split_k <= 1). */
+size_t pamk_matmul_workspace_bytes(int64_t batch, int64_t M, int64_t N, int split_k);
+/* The split the library would choose for split_k = 0 given unlimited workspace. */
+int pamk_matmul_auto_split(int64_t batch, int64_t M, int64_t N, int64_t K);
+
+/* Exact-gradient product: out[z][i][j] = sum_k pam_bwd(D[z][i][j], other, delta) with
+ * (other, delta) = (R[k][j], L[i][k]) if delta_l else (L[i][k], R[k][j]).
+ * Replaces pam_matmul_bwd / pam_bmm_bwd: pam_matmul_bwd_caller, cuda_kernels.cu:834-927. */
+int pamk_matmul_bwd(const float* L, const float* R, const float* D, float* out,
+                    int64_t batch, int64_t M, int64_t N, int64_t K,
+                    int64_t sLb, int64_t sLm, int64_t sLk,
+                    int64_t sRb, int64_t sRk, int64_t sRn,
+                    int64_t sDb, int64_t sDm, int64_t sDn,
+                    int delta_l, float offset, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,98 @@
+"""ctypes binding of ``libpam_b200.so`` (the C ABI declared in ``include/pam_b200.h``).
+
+There is no fallback: if the library has not been built, or a call returns an error status, an
+exception is raised.  PyTorch only supplies device memory and the stream; every operation below
+runs in the library's own sm_100a kernels.
+"""
+import ctypes
+import pathlib
+
+import torch
+
+_PKG = pathlib.Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libpam_b200.so"
+
+FULL, SCALAR, ROW, COL, IMM = 0, 1, 2, 3, 4
+MUL_PAM, MUL_STANDARD = 0, 1
+
+_p, _i, _i64, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_size_t
+_operand = [_p, _i, _f]
+
+_SIGNATURES = {
+    "pamk_status_string": (ctypes.c_char_p, [_i]),
+    "pamk_last_cuda_error": (_i, []),
+    "pamk_abi_version": (_i, []),
+    "pamk_pam_fwd": (_i, _operand * 2 + [_p, _i64, _i64, _f, _p]),
+    "pamk_pad_fwd": (_i, _operand * 2 + [_p, _i64, _i64, _f, _p]),
+    "pamk_pam_bwd": (_i, _operand * 3 + [_p, _i64, _i64, _f, _p]),
+    "pamk_pad_bwd": (_i, _operand * 3 + [_p, _i64, _i64, _f, _p]),
+    "pamk_pa_exp_fwd": (_i, [_p, _p, _i64, _f, _f, _p]),
+    "pamk_pa_exp_bwd": (_i, [_p, _p, _p, _i64, _f, _f, _p]),
+    "pamk_pa_log_fwd": (_i, [_p, _p, _i64, _f, _f, _p]),
+    "pamk_pa_log_bwd": (_i, [_p, _p, _p, _i64, _f, _f, _p]),
+    "pamk_matmul": (_i, [_i, _p, _p, _p] + [_i64] * 10 + [_f, _i, _p, _sz, _p]),
+    "pamk_matmul_workspace_bytes": (_sz, [_i64, _i64, _i64, _i]),
+    "pamk_matmul_auto_split": (_i, [_i64] * 4),
+    "pamk_matmul_bwd": (_i, [_p] * 4 + [_i64] * 13 + [_i, _f, _p]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library; raises if it was never built (``python -m pam_b200.build``)."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing. pam_b200 has no fallback path: build the CUDA kernels first "
+                "with `python -m pam_b200.build` (needs nvcc).")
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def exported_names():
+    return list(_SIGNATURES)
+
+
+class PamKernelError(RuntimeError):
+    pass
+
+
+def check(status, what):
+    if status != 0:
+        handle = lib()
+        msg = handle.pamk_status_string(status).decode()
+        if status == -5:
+            msg += f" [cudaError {handle.pamk_last_cuda_error()}]"
+        raise PamKernelError(f"{what}: {msg}")
+
+
+def require_cuda(*tensors):
+    """All tensor operands must be fp32-convertible CUDA tensors on one device."""
+    dev = None
+    for t in tensors:
+        if not isinstance(t, torch.Tensor):
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("pam_b200 runs on CUDA tensors only (there is no CPU path); got a "
+                               f"{t.device.type} tensor")
+        if dev is not None and t.device != dev:
+            raise RuntimeError(f"operands on different devices: {dev} and {t.device}")
+        dev = t.device
+    if dev is None:
+        raise RuntimeError("at least one operand must be a CUDA tensor")
+    return dev
+
+
+def stream_ptr(device):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def device_guard(device):
+    """Makes `device` current for the duration of a kernel launch."""
+    return torch.cuda.device(device)
