@@ -37,6 +37,8 @@ const char* pamk_status_string(int status);
 int pamk_last_cuda_error(void);
 /* ABI version of this header (bumped when a signature changes). */
 int pamk_abi_version(void);
+/* Number of kernels this library has launched in this process so far (all threads). */
+long long pamk_launch_count(void);
 
 /* ---- operand descriptors for the elementwise entry points ---------------------------------
  * The reference broadcasts in Python and materialises the expanded operand
@@ -118,6 +120,16 @@ int pamk_matmul_bwd(const float* L, const float* R, const float* D, float* out,
                     int64_t sRb, int64_t sRk, int64_t sRn,
                     int64_t sDb, int64_t sDm, int64_t sDn,
                     int delta_l, float offset, void* stream);
+
+/* ---- roofline measurement --------------------------------------------------------------------
+ * No counterpart in the reference.  Runs register-only chains of the instructions a PAM
+ * multiply-accumulate is made of and reports how many chain steps ran in how many milliseconds;
+ * variant 0 fp32 add, 1 int32 add, 2 int add + fp add (1:1), 3 int multiply-add + fp add,
+ * 4 alternating int add / multiply-add + fp add, 5 fp32 fma, 6 the checked loop's mix
+ * (add, multiply, compare, predicated add).  `scratch` is one device int.  This call
+ * synchronises (CUDA events on `stream`). */
+int pamk_issue_rate(int variant, int iters, int ctas_per_sm, int* scratch, float* elapsed_ms,
+                    double* chain_steps, void* stream);
 
 #ifdef __cplusplus
 }

@@ -22,6 +22,7 @@ _SIGNATURES = {
     "pamk_status_string": (ctypes.c_char_p, [_i]),
     "pamk_last_cuda_error": (_i, []),
     "pamk_abi_version": (_i, []),
+    "pamk_launch_count": (ctypes.c_longlong, []),
     "pamk_pam_fwd": (_i, _operand * 2 + [_p, _i64, _i64, _f, _p]),
     "pamk_pad_fwd": (_i, _operand * 2 + [_p, _i64, _i64, _f, _p]),
     "pamk_pam_bwd": (_i, _operand * 3 + [_p, _i64, _i64, _f, _p]),
@@ -34,6 +35,7 @@ _SIGNATURES = {
     "pamk_matmul_workspace_bytes": (_sz, [_i64, _i64, _i64, _i]),
     "pamk_matmul_auto_split": (_i, [_i64] * 4),
     "pamk_matmul_bwd": (_i, [_p] * 4 + [_i64] * 13 + [_i, _f, _p]),
+    "pamk_issue_rate": (_i, [_i, _i, _i, _p, ctypes.POINTER(_f), ctypes.POINTER(ctypes.c_double), _p]),
 }
 
 _lib = None

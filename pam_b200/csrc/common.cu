@@ -1,8 +1,13 @@
 #include "common.cuh"
 
+#include <atomic>
+
 namespace pamk {
 
 static thread_local int g_last_cuda_error = 0;
+static std::atomic<long long> g_launches{0};
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int record_cuda_error(cudaError_t err) {
     g_last_cuda_error = (int)err;
@@ -40,5 +45,7 @@ const char* pamk_status_string(int status) {
 int pamk_last_cuda_error(void) { return pamk::g_last_cuda_error; }
 
 int pamk_abi_version(void) { return 1; }
+
+long long pamk_launch_count(void) { return pamk::g_launches.load(std::memory_order_relaxed); }
 
 }

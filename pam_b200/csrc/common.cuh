@@ -15,8 +15,12 @@ int sm_count();
 // Records a failed CUDA call for pamk_last_cuda_error() and returns PAMK_ERR_CUDA.
 int record_cuda_error(cudaError_t err);
 
+// Counts kernel launches made by this library (read by pamk_launch_count()).
+void count_launch();
+
 inline int check_launch() {
     const cudaError_t err = cudaGetLastError();
+    count_launch();
     return err == cudaSuccess ? PAMK_OK : record_cuda_error(err);
 }
 

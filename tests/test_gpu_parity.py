@@ -1,0 +1,399 @@
+"""Parity of the CUDA kernels (through the C ABI) with the reference: committed fixtures generated
+from the reference's own code, and the CPU oracle on seeded inputs at sizes it finishes quickly.
+
+Bars: per-element operations bit-exact (NaN payloads aside); matrix products without split-K
+bit-exact as well (same products, same k order, one accumulator); with split-K, and for values
+that went through an ordinary fp32 row reduction, within a stated tolerance."""
+import math
+
+import pytest
+import torch
+
+import parity_cases as cases
+from conftest import assert_bits_equal, assert_close_nan, bits_equal
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def pam():
+    import pam_b200
+    assert torch.cuda.is_available(), "gpu-marked tests need a CUDA device"
+    return pam_b200
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda", 0)
+
+
+@pytest.fixture(scope="module")
+def K(oracle):
+    return oracle.kernels()
+
+
+SPECIALS = [0.0, -0.0, 1e-40, -1e-40, 1.4e-45, -1.4e-45, 1e30, -1e30, 1e-30, -1e-30]
+
+
+def inject(t, frac, g, extra=()):
+    """Overwrites a fixed fraction of entries with a cycle of special values (zeros, denormals,
+    +-1e30, +-1e-30): the value distribution of the scaling-sweep configuration."""
+    flat = t.reshape(-1)
+    count = max(1, int(flat.numel() * frac))
+    idx = torch.randperm(flat.numel(), generator=g)[:count]
+    vals = torch.tensor(SPECIALS + list(extra), dtype=torch.float32)
+    flat[idx] = vals[torch.arange(count) % vals.numel()]
+    return t
+
+
+# ---- fixtures generated from the reference -------------------------------------------------------
+
+@pytest.mark.parametrize("oname,mode", cases.MODES)
+def test_golden_mul_div(pam, golden, dev, oname, mode):
+    cases.mul_div(pam, golden, dev, oname, mode)
+
+
+def test_golden_broadcast(pam, golden, dev):
+    cases.broadcast(pam, golden, dev, exact_sums=False)
+
+
+@pytest.mark.parametrize("base", ["e", "2", "10"])
+@pytest.mark.parametrize("oname,mode", cases.MODES)
+def test_golden_exp_log(pam, golden, dev, base, oname, mode):
+    cases.exp_log(pam, golden, dev, base, oname, mode)
+
+
+def test_golden_pow(pam, golden, dev):
+    cases.pow_(pam, golden, dev)
+
+
+@pytest.mark.parametrize("tag,oname", [("ref21", "none"), ("ref20", "none"), ("rand", "none"), ("rand", "o1")])
+@pytest.mark.parametrize("mode", ["exact", "approx"])
+def test_golden_matmul(pam, golden, dev, tag, oname, mode):
+    cases.matmul(pam, golden, dev, tag, oname, mode)
+
+
+def test_golden_layouts_bmm_linear(pam, golden, dev):
+    cases.matmul_layouts(pam, golden, dev)
+    cases.bmm(pam, golden, dev)
+    cases.linear_module(pam, golden, dev, exact_sums=False)
+
+
+@pytest.mark.parametrize("oname,mode", cases.MODES)
+def test_golden_reductions_layer_norm(pam, golden, dev, oname, mode):
+    cases.reductions(pam, golden, dev, oname, mode, exact_sums=False)
+    cases.layer_norm(pam, golden, dev, oname, mode, exact_sums=False)
+
+
+def test_golden_cross_entropy_and_adam(pam, golden, dev):
+    from pam_b200 import factories, optim
+    cases.cross_entropy(pam, factories, golden, dev, exact_sums=False)
+    cases.adam(optim, golden, dev)
+
+
+def test_reference_known_answers_on_gpu(pam, dev):
+    # pam/test_pam.py:13-29 and :36-43, run as the reference runs them (allclose / non-finite)
+    abc = torch.tensor([
+        [1.0, 1.0, 1.0], [1.2345, 1.0, 1.2345], [1.2345, 32.0, 32.0 * 1.2345],
+        [-1.2345, 32.0, -32.0 * 1.2345], [1.2345, -32.0, -32.0 * 1.2345], [-1.2345, -32.0, 32.0 * 1.2345],
+        [1.0, 0.0, 0.0], [0.0, -1.0, -0.0], [1.5, 1.5, 2.0], [1.3, -1.3, -1.6],
+        [4.5, 3.0, 8 * (1 + (4.5 - 4) / 4 + (3.0 - 2) / 2)], [-6.0, 3.0, -16.0],
+        [-3.5, -3.5, 8 * (1 + (3.5 - 2) / 2 + (3.5 - 2) / 2 - 1)], [1e-30, 1e-30, 0.0], [1e-30, -1e-30, -0.0],
+    ], device=dev)
+    for method in (pam.cuda_bindings.pam, pam.native.pam):
+        assert torch.allclose(abc[:, 2], method(abc[:, 0].contiguous(), abc[:, 1].contiguous()))
+    ab = torch.tensor([[1e30, 1e30], [1e30, -1e30], [float("-inf"), 1e-20], [float("nan"), -1e-20],
+                       [float("inf"), 0.0], [float("nan"), 0.0]], device=dev)
+    assert (~pam.cuda_bindings.pam(ab[:, 0].contiguous(), ab[:, 1].contiguous()).isfinite()).all()
+
+
+# ---- elementwise kernels against the oracle --------------------------------------------------------
+
+def _wide(n, g, spread=40):
+    return torch.randn(n, generator=g) * torch.exp2(torch.randint(-spread, spread, (n,), generator=g).float())
+
+
+@pytest.mark.parametrize("n", [1, 3, 4, 5, 1023, 4096, 1_000_003])
+@pytest.mark.parametrize("offset", [1.0, 1.0552])
+def test_elementwise_sizes_and_specials(pam, K, dev, n, offset):
+    g = torch.Generator().manual_seed(n)
+    a, b, dc = inject(_wide(n, g), 0.05, g), inject(_wide(n, g), 0.05, g), _wide(n, g, 10)
+    ck = pam.cuda_bindings.cuda_kernels
+    ad, bd, dd = a.to(dev), b.to(dev), dc.to(dev)
+    assert_bits_equal(ck.pam_fwd(ad, bd, offset), K.pam_fwd(a, b, offset), "pam")
+    assert_bits_equal(ck.pad_fwd(ad, bd, offset), K.pad_fwd(a, b, offset), "pad")
+    assert_bits_equal(ck.pam_bwd(ad, bd, dd, offset), K.pam_bwd(a, b, dc, offset), "pam_bwd")
+    assert_bits_equal(ck.pad_bwd(ad, bd, dd, offset), K.pad_bwd(a, b, dc, offset), "pad_bwd")
+
+
+def test_elementwise_raw_bit_patterns(pam, K, dev):
+    g = torch.Generator().manual_seed(11)
+    n = 2_000_000
+    a, b, dc = (torch.randint(-2**31, 2**31 - 1, (n,), generator=g, dtype=torch.int64).to(torch.int32)
+                .view(torch.float32) for _ in range(3))
+    ck = pam.cuda_bindings.cuda_kernels
+    ad, bd, dd = a.to(dev), b.to(dev), dc.to(dev)
+    assert_bits_equal(ck.pam_fwd(ad, bd, 1.0), K.pam_fwd(a, b, 1.0))
+    assert_bits_equal(ck.pad_fwd(ad, bd, 1.0), K.pad_fwd(a, b, 1.0))
+    assert_bits_equal(ck.pam_bwd(ad, bd, dd, 0.97), K.pam_bwd(a, b, dc, 0.97))
+    assert_bits_equal(ck.pad_bwd(ad, bd, dd, 0.97), K.pad_bwd(a, b, dc, 0.97))
+
+
+def test_elementwise_misaligned_views_and_guard_bands(pam, K, dev):
+    """Operands that start 4 bytes off a 16-byte boundary take the scalar path; the kernel must
+    not write outside its output (checked with canaries around a hand-placed output)."""
+    from pam_b200 import _lib
+    g = torch.Generator().manual_seed(5)
+    n = 10_001
+    a, b = _wide(n + 1, g), _wide(n + 1, g)
+    ad, bd = a.to(dev)[1:], b.to(dev)[1:]
+    assert ad.data_ptr() % 16 == 4
+    want = K.pam_fwd(a[1:], b[1:], 1.0)
+    assert_bits_equal(pam.cuda_bindings.cuda_kernels.pam_fwd(ad, bd, 1.0), want)
+    for lead in (64, 65):                     # aligned and misaligned output start
+        buf = torch.full((lead + n + 64,), 12345.0, device=dev)
+        out = buf[lead:lead + n]
+        h = _lib.lib()
+        _lib.check(h.pamk_pam_fwd(ad.data_ptr(), 0, 0.0, bd.data_ptr(), 0, 0.0, out.data_ptr(), n, 0, 1.0,
+                                  torch.cuda.current_stream().cuda_stream), "pam_fwd")
+        assert_bits_equal(out, want)
+        assert bool((buf[:lead] == 12345.0).all()) and bool((buf[lead + n:] == 12345.0).all())
+
+
+@pytest.mark.parametrize("inner", [1, 4, 7, 192, 1000])
+def test_elementwise_broadcast_kinds(pam, K, dev, inner):
+    g = torch.Generator().manual_seed(inner)
+    rows = 37
+    m, row, col = _wide(rows * inner, g).view(rows, inner), _wide(inner, g), _wide(rows, g).view(rows, 1)
+    ck = pam.cuda_bindings.cuda_kernels
+    md, rd, cd = m.to(dev), row.to(dev), col.to(dev)
+    for other, od in ((row, rd), (col, cd), (col[3, 0], cd[3, 0]), (0.3, 0.3)):
+        full = other.expand(rows, inner).contiguous() if isinstance(other, torch.Tensor) else torch.full((rows, inner), other)
+        assert_bits_equal(ck.pam_fwd(md, od, 1.0), K.pam_fwd(m, full, 1.0), "pam rhs")
+        assert_bits_equal(ck.pad_fwd(od, md, 1.0), K.pad_fwd(full, m, 1.0), "pad lhs")
+        assert_bits_equal(ck.pam_bwd(md, od, md, 1.0), K.pam_bwd(m, full, m, 1.0), "pam_bwd")
+        assert_bits_equal(ck.pad_bwd(md, od, od, 1.0), K.pad_bwd(m, full, full, 1.0), "pad_bwd")
+    # an expanded (stride-0) view is described, not materialised, and gives the same bits
+    assert_bits_equal(ck.pam_fwd(md, cd.expand(rows, inner), 1.0), K.pam_fwd(m, col.expand(rows, inner).contiguous(), 1.0))
+
+
+def _near_pow2_below(x):
+    """Inputs within 2 ulp below a power of two: floor(log2f(x)) legitimately depends on the
+    libm in use (device vs host), and with it the piecewise-affine segment."""
+    bits = x.view(torch.int32) & 0x7FFFFFFF
+    return (bits & 0x007FFFFF) >= 0x007FFFFE
+
+
+@pytest.mark.parametrize("base", [2.0, math.e, 10.0, 0.5])
+@pytest.mark.parametrize("offset", [1.0, 1.0552])
+def test_exp_log_against_oracle(pam, K, dev, base, offset):
+    g = torch.Generator().manual_seed(21)
+    n = 500_000
+    x = torch.cat([torch.randn(n, generator=g) * 30, _wide(n, g, 60), inject(torch.randn(1000, generator=g), 0.5, g,
+                  extra=(float("inf"), float("-inf"), float("nan"), 127.5, -126.5, -149.5, 128.0)),
+                   torch.arange(-170, 140).float(), torch.arange(-170, 140).float() - 2.0 ** -18])
+    dy = _wide(x.numel(), g, 30)
+    ck = pam.cuda_bindings.cuda_kernels
+    xd, dd = x.to(dev), dy.to(dev)
+    assert_bits_equal(ck.pa_exp_fwd(xd, base, offset), K.pa_exp_fwd(x, base, offset), "exp")
+    assert_bits_equal(ck.pa_exp_bwd(xd, dd, base, offset), K.pa_exp_bwd(x, dy, base, offset), "exp_bwd")
+    # log: every binade, both ends of each, plus random magnitudes
+    e = torch.arange(0, 255, dtype=torch.int32)
+    m = torch.tensor([0, 1, 2, 0x400000, 0x7FFFFD, 0x7FFFFE, 0x7FFFFF], dtype=torch.int32)
+    grid = ((e[:, None] << 23) | m[None, :]).reshape(-1).view(torch.float32)
+    xl = torch.cat([grid, _wide(n, g, 60).abs(), torch.tensor([0.0, -1.0, float("inf"), float("nan")])])
+    dl = _wide(xl.numel(), g, 30)
+    got, want = ck.pa_log_fwd(xl.to(dev), base, offset).cpu(), K.pa_log_fwd(xl, base, offset)
+    gotb, wantb = ck.pa_log_bwd(xl.to(dev), dl.to(dev), base, offset).cpu(), K.pa_log_bwd(xl, dl, base, offset)
+    sure = ~_near_pow2_below(xl)
+    assert_bits_equal(got[sure], want[sure], "log")
+    assert_bits_equal(gotb[sure], wantb[sure], "log_bwd")
+    # just below a power of two either segment is a legitimate answer; they meet there, so the
+    # values agree closely even when the bits do not
+    edge = ~sure & want.isfinite()
+    assert_close_nan(got[edge], want[edge], 1e-5, 1e-6, "log at binade edge")
+
+
+# ---- matrix products against the oracle -------------------------------------------------------------
+
+SHAPES = [(1, 1, 1), (5, 3, 4), (33, 31, 1), (17, 19, 23), (128, 128, 16), (129, 130, 17), (257, 64, 100),
+          (64, 300, 48), (200, 192, 192)]
+
+
+def _layouts(A, B):
+    yield "rm x rm", A, B
+    yield "rm x cm", A, B.T.contiguous().T
+    yield "cm x rm", A.T.contiguous().T, B
+    yield "cm x cm", A.T.contiguous().T, B.T.contiguous().T
+
+
+@pytest.mark.parametrize("M,N,Kdim", SHAPES)
+def test_matmul_shapes_layouts_bit_exact(pam, K, dev, M, N, Kdim):
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    A, B = torch.randn(M, Kdim, generator=g), torch.randn(Kdim, N, generator=g) * 0.02
+    want = K.pam_matmul_fwd(A, B)
+    std = K.standard_matmul(A, B)
+    ck = pam.cuda_bindings.cuda_kernels
+    for name, a, b in _layouts(A.to(dev), B.to(dev)):
+        assert_bits_equal(ck.pam_matmul_fwd(a, b, True, True, 1.0), want, f"pam {name}")
+        assert_bits_equal(ck.standard_matmul(a, b), std, f"standard {name}")
+    D = torch.randn(M, N, generator=g)
+    for delta_l in (True, False):
+        wantb = K.pam_matmul_bwd(A, B, D, True, True, delta_l, 1.0552)
+        for name, a, b in _layouts(A.to(dev), B.to(dev)):
+            assert_bits_equal(ck.pam_matmul_bwd(a, b, D.to(dev), True, True, delta_l, 1.0552), wantb,
+                              f"bwd {name} delta_l={delta_l}")
+
+
+@pytest.mark.parametrize("frac", [0.01, 0.3])
+@pytest.mark.parametrize("offset", [1.0, 1.0552])
+def test_matmul_special_values_bit_exact(pam, K, dev, frac, offset):
+    """Zeros, denormals, +-1e30 / +-1e-30, inf and NaN in the operands: the hoisted range rule must
+    reproduce flush-to-+0, NaN-on-overflow and raw-bit denormal products exactly."""
+    g = torch.Generator().manual_seed(int(frac * 100))
+    A = inject(torch.randn(150, 260, generator=g), frac, g)
+    B = inject(torch.randn(260, 140, generator=g), frac, g)
+    A[7, 100] = float("inf")
+    B[33, 5] = float("nan")
+    A[100:110] = 0.0                    # an all-zero row block (padding-like)
+    want = K.pam_matmul_fwd(A, B, True, True, offset)
+    assert want.isnan().any() and (~want.isnan()).any()
+    for name, a, b in _layouts(A.to(dev), B.to(dev)):
+        assert_bits_equal(pam.cuda_bindings.cuda_kernels.pam_matmul_fwd(a, b, True, True, offset), want, name)
+
+
+def test_matmul_tiny_and_huge_magnitudes(pam, K, dev):
+    """Operands whose exponent ranges make the per-slab classification take each branch: all
+    products far in range, products straddling the 1e-37 flush threshold, and straddling 1e37."""
+    g = torch.Generator().manual_seed(3)
+    for scale_a, scale_b in ((1.0, 1.0), (1e-19, 1e-19), (1e-18, 3e-20), (1e18, 1e19), (3e18, 3e18), (1e-30, 1e30)):
+        A = torch.randn(96, 80, generator=g) * scale_a
+        B = torch.randn(80, 72, generator=g) * scale_b
+        want = K.pam_matmul_fwd(A, B)
+        got = pam.cuda_bindings.cuda_kernels.pam_matmul_fwd(A.to(dev), B.to(dev), True, True, 1.0)
+        assert_bits_equal(got, want, f"scales {scale_a} x {scale_b}")
+
+
+def test_bmm_bit_exact_and_guard_bands(pam, K, dev):
+    from pam_b200 import _lib
+    g = torch.Generator().manual_seed(8)
+    A, B = torch.randn(11, 13, 15, generator=g), torch.randn(11, 15, 19, generator=g)
+    want = K.pam_bmm_fwd(A, B)
+    ck = pam.cuda_bindings.cuda_kernels
+    assert_bits_equal(ck.pam_bmm_fwd(A.to(dev), B.to(dev), True, True, 1.0), want)
+    # batch-transposed views (attention's k.transpose(-1, -2))
+    Bt = B.transpose(1, 2).contiguous().transpose(1, 2)
+    assert_bits_equal(ck.pam_bmm_fwd(A.to(dev), Bt.to(dev), True, True, 1.0), want)
+    D = torch.randn(11, 13, 19, generator=g)
+    assert_bits_equal(ck.pam_bmm_bwd(A.to(dev), B.to(dev), D.to(dev), True, True, True, 1.0),
+                      K.pam_bmm_bwd(A, B, D, True, True, True, 1.0))
+    # output written in place between canaries
+    count = 11 * 13 * 19
+    buf = torch.full((256 + count + 256,), -7.0, device=dev)
+    out = buf[256:256 + count]
+    Ad, Bd = A.to(dev), B.to(dev)
+    _lib.check(_lib.lib().pamk_matmul(0, Ad.data_ptr(), Bd.data_ptr(), out.data_ptr(), 11, 13, 19, 15,
+                                      *Ad.stride(), *Bd.stride(), 1.0, 1, None, 0,
+                                      torch.cuda.current_stream().cuda_stream), "matmul")
+    assert_bits_equal(out.view(11, 13, 19), want)
+    assert bool((buf[:256] == -7.0).all()) and bool((buf[256 + count:] == -7.0).all())
+
+
+def _sum_abs_products(K, A, B):
+    return K.pam_matmul_fwd(A.abs(), B.abs()).double()
+
+
+@pytest.mark.parametrize("split", [2, 5, 16])
+def test_matmul_split_k_within_tolerance(pam, K, dev, split):
+    """Split-K adds the same bit-exact products in a different association.  Bound for any
+    order: |C - S| <= 2 * K * 2^-24 * sum|p_k|  (S the exact sum of the products)."""
+    from pam_b200 import cuda_bindings as cb
+    g = torch.Generator().manual_seed(split)
+    M, N, Kdim = 100, 70, 1000
+    A, B = torch.randn(M, Kdim, generator=g), torch.randn(Kdim, N, generator=g)
+    seq = K.pam_matmul_fwd(A, B)
+    got = cb._matmul(0, A.to(dev), B.to(dev), 1.0, 2, split_k=split).cpu()
+    bound = 2 * Kdim * 2.0 ** -24 * _sum_abs_products(K, A, B)
+    err = (got.double() - seq.double()).abs()
+    assert bool((err <= 2 * bound).all())          # both sums are within `bound` of S
+    assert float((err / (2.0 ** -24 * _sum_abs_products(K, A, B))).max()) < 4 * math.sqrt(Kdim)
+    # and it is deterministic
+    again = cb._matmul(0, A.to(dev), B.to(dev), 1.0, 2, split_k=split).cpu()
+    assert torch.equal(got, again)
+
+
+def test_config1_matmul_forward_and_approx_backward(pam, K, dev):
+    """BASELINE config 1: A[512x1024] . B[1024x512], N(0,1), forward plus approx_bwd backward with
+    N(0,1) grad_out; per-product results on a sampled block and all three products bit-exact."""
+    g = torch.Generator().manual_seed(1)
+    A, B, G = torch.randn(512, 1024, generator=g), torch.randn(1024, 512, generator=g), torch.randn(512, 512, generator=g)
+    pam.set_strict_k_order(True)
+    try:
+        Ad, Bd = A.to(dev).requires_grad_(), B.to(dev).requires_grad_()
+        C = pam.matmul(Ad, Bd, approx_bwd=True)
+        C.backward(G.to(dev))
+    finally:
+        pam.set_strict_k_order(False)
+    assert_bits_equal(C, K.pam_matmul_fwd(A, B), "C")
+    assert_bits_equal(Ad.grad, K.pam_matmul_fwd(G, B.T), "dA")
+    assert_bits_equal(Bd.grad, K.pam_matmul_fwd(A.T, G), "dB")
+    # per-product check on rows 0..63 x all K x cols 0..63 through the elementwise kernel
+    prod = pam.mul(A[:64, :, None].to(dev), B[None, :, :64].to(dev))
+    want = K.pam_fwd(A[:64, :, None].expand(64, 1024, 64).contiguous(), B[None, :, :64].expand(64, 1024, 64).contiguous(), 1.0)
+    assert_bits_equal(prod, want, "per-product")
+
+
+def test_deit_linear_set_bit_exact_on_row_sample(pam, K, dev):
+    """BASELINE config 2 shapes (M = 12608 tokens, 192->576, 192->192, 192->768, 768->192,
+    trunc-normal(0.02) weights): full-size products on the GPU, checked bit for bit on a sample of
+    rows against the oracle, forward and both approx_bwd gradients."""
+    g = torch.Generator().manual_seed(2)
+    M = 12608
+    rows = torch.randperm(M, generator=g)[:96]
+    pam.set_strict_k_order(True)
+    try:
+        for k_in, n_out in ((192, 576), (192, 192), (192, 768), (768, 192)):
+            X = torch.randn(M, k_in, generator=g)
+            W = torch.nn.init.trunc_normal_(torch.empty(n_out, k_in), std=0.02, generator=g)
+            G = torch.randn(M, n_out, generator=g)
+            Xd, Wd = X.to(dev).requires_grad_(), W.to(dev).requires_grad_()
+            Y = pam.linear(Xd, Wd, approx_bwd=True)
+            Y.backward(G.to(dev))
+            assert_bits_equal(Y[rows.to(dev)], K.pam_matmul_fwd(X[rows], W.T), f"Y {k_in}->{n_out}")
+            assert_bits_equal(Xd.grad[rows.to(dev)], K.pam_matmul_fwd(G[rows], W), f"dX {k_in}->{n_out}")
+            cols = torch.arange(0, k_in, 7)
+            assert_bits_equal(Wd.grad[:, cols.to(dev)], K.pam_matmul_fwd(G.T, X[:, cols]), f"dW {k_in}->{n_out}")
+    finally:
+        pam.set_strict_k_order(False)
+
+
+def test_square_gemm_4096_with_specials_sampled(pam, K, dev):
+    """Scaling-sweep configuration at 4096^3 with 1% injected special values: a 48x48 block of the
+    output (full K) must match the oracle bit for bit, and permuting the rows of A must permute the
+    rows of C (a size-independent property of the per-output summation)."""
+    g = torch.Generator().manual_seed(4)
+    n = 4096
+    A = inject(torch.randn(n, n, generator=g), 0.01, g)
+    B = inject(torch.randn(n, n, generator=g), 0.01, g)
+    Ad, Bd = A.to(dev), B.to(dev)
+    ck = pam.cuda_bindings.cuda_kernels
+    C = ck.pam_matmul_fwd(Ad, Bd, True, True, 1.0)
+    r = torch.randperm(n, generator=g)[:48]
+    c = torch.randperm(n, generator=g)[:48]
+    assert_bits_equal(C[r.to(dev)][:, c.to(dev)], K.pam_matmul_fwd(A[r], B[:, c]), "sampled block")
+    perm = torch.randperm(n, generator=g).to(dev)
+    Cp = ck.pam_matmul_fwd(Ad[perm], Bd, True, True, 1.0)
+    assert bool(bits_equal(Cp, C[perm]).all())
+
+
+def test_abi_rejects_bad_arguments_on_gpu(pam, dev):
+    from pam_b200 import _lib
+    h = _lib.lib()
+    x = torch.ones(64, device=dev)
+    s = torch.cuda.current_stream().cuda_stream
+    assert h.pamk_pam_fwd(x.data_ptr(), 9, 0.0, x.data_ptr(), 0, 0.0, x.data_ptr(), 64, 0, 1.0, s) == -1
+    assert h.pamk_pam_fwd(x.data_ptr(), 2, 0.0, x.data_ptr(), 0, 0.0, x.data_ptr(), 64, 5, 1.0, s) == -1   # 64 % 5
+    assert h.pamk_matmul(0, x.data_ptr(), x.data_ptr(), x.data_ptr(), 1, 4, 4, 4, 0, 8, 2, 0, 4, 1, 1.0, 1, None, 0, s) == -3
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        pam.mul(torch.ones(3), torch.ones(3))
+    torch.cuda.synchronize()
