@@ -110,6 +110,10 @@ int pamk_matmul(int mul_kind, const float* A, const float* B, float* C,
 size_t pamk_matmul_workspace_bytes(int64_t batch, int64_t M, int64_t N, int split_k);
 /* The split the library would choose for split_k = 0 given unlimited workspace. */
 int pamk_matmul_auto_split(int64_t batch, int64_t M, int64_t N, int64_t K);
+/* Tuning / testing knob (process-wide, not thread-safe): the PAM product picks a 128x128 or a
+ * 64x64 CTA tile per problem; 0 = by cost model (default), 1 = always 128x128, 2 = always 64x64.
+ * Results do not depend on the tile. */
+int pamk_matmul_set_tile_policy(int policy);
 
 /* Exact-gradient product: out[z][i][j] = sum_k pam_bwd(D[z][i][j], other, delta) with
  * (other, delta) = (R[k][j], L[i][k]) if delta_l else (L[i][k], R[k][j]).
@@ -120,6 +124,26 @@ int pamk_matmul_bwd(const float* L, const float* R, const float* D, float* out,
                     int64_t sRb, int64_t sRk, int64_t sRn,
                     int64_t sDb, int64_t sDm, int64_t sDn,
                     int delta_l, float offset, void* stream);
+
+/* ---- fused layer normalisation (pam_ln) -----------------------------------------------------------
+ * Replaces the chain of launches that pam/pam_ops.py:350-378 (layer_norm) issues through
+ * pam/cuda_bindings.py — pam_fwd/pad_fwd/pa_log_fwd/pa_exp_fwd forward and their gradient kernels
+ * backward — with one kernel each way, rounding where the chain rounds:
+ *   mu = pad(sum x, n); c = x - mu; var = pad(sum pam(c,c), n); denom = pow(var + eps, 0.5);
+ *   y = pam(pad(c, denom), weight) + bias.
+ * x, y, dy, dx are [rows, width] contiguous; weight / bias / dweight / dbias are [width] or NULL.
+ * width <= pamk_layer_norm_max_width().  Row sums are warp-shuffle trees, so y and the gradients
+ * agree with the reference up to the association of those fp32 sums.
+ * The backward needs scratch (per-CTA column sums for dweight / dbias) when either is requested:
+ * pamk_layer_norm_bwd_workspace_bytes(rows, width) bytes, 16-byte aligned.
+ * approx_bwd selects the reference's approximate (PAM-product) or exact (slope) gradient rules. */
+int pamk_layer_norm_max_width(void);
+int pamk_layer_norm_fwd(const float* x, const float* weight, const float* bias, float* y,
+                        int64_t rows, int64_t width, float eps, float offset, void* stream);
+size_t pamk_layer_norm_bwd_workspace_bytes(int64_t rows, int64_t width);
+int pamk_layer_norm_bwd(const float* x, const float* weight, const float* dy, float* dx,
+                        float* dweight, float* dbias, int64_t rows, int64_t width, float eps, float offset,
+                        int approx_bwd, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- roofline measurement --------------------------------------------------------------------
  * No counterpart in the reference.  Runs register-only chains of the instructions a PAM

@@ -1,8 +1,7 @@
 // Elementwise PAM kernels: pam / pad forward and exact backward, base^x and log_base(x).
 //
 // HBM-bound (8-16 bytes per element), so the design is about bytes in flight: 128-bit loads and
-// stores, two independent vectors per thread per trip, a grid that is a whole number of waves
-// over the SMs, and broadcast operands (scalars, row vectors, per-row values) read in place
+// stores, two independent vectors per operand per thread, full occupancy, and broadcast operands (scalars, row vectors, per-row values) read in place
 // instead of being expanded to full size as the reference does
 // (epfml/pam pam/cuda_kernels.cu:141-516, one thread per element over .flatten()ed inputs).
 #include "common.cuh"
@@ -88,22 +87,25 @@ struct LogBwd {
 };
 
 constexpr int kThreads = 256;
+constexpr int kPerThread = 8;                       // two 128-bit vectors per operand per thread
+constexpr int kPerBlock = kThreads * kPerThread;
 
+// One CTA covers 2048 consecutive outputs: thread t takes the four at 4t and the four at
+// 1024 + 4t, so each 128-bit access of a warp is one contiguous 512-byte run.  All loads of a
+// thread are issued before its first use.  The grid is sized to the data (no persistent loop),
+// with 32 registers or fewer per thread so that every SM holds its full 2048 threads.
 template <class Op, int NIN, bool VEC>
-__global__ void __launch_bounds__(kThreads) ew_kernel(Op op, Operand o0, Operand o1, Operand o2,
-                                                      float* __restrict__ out, Shape s) {
+__global__ void __launch_bounds__(kThreads, NIN > 2 ? 6 : 8) ew_kernel(Op op, Operand o0, Operand o1, Operand o2,
+                                                         float* __restrict__ out, Shape s) {
     const float s0 = splat_value(o0);
     const float s1 = NIN > 1 ? splat_value(o1) : 0.0f;
     const float s2 = NIN > 2 ? splat_value(o2) : 0.0f;
-    const int64_t tid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    const int64_t nthreads = (int64_t)gridDim.x * kThreads;
+    const int64_t base = (int64_t)blockIdx.x * kPerBlock;
     if (VEC) {
         const int64_t n4 = s.n & ~(int64_t)3;
-        const int64_t stride = nthreads * 4;
-        for (int64_t i = tid * 4; i < n4; i += 2 * stride) {
-            const int64_t j = i + stride;
-            const bool two = j < n4;
-            // issue every load of the trip before the first use
+        const int64_t i = base + threadIdx.x * 4, j = i + kThreads * 4;
+        const bool one = i < n4, two = j < n4;
+        if (one) {
             const float4 a0 = load4(o0, i, s, s0);
             const float4 b0 = NIN > 1 ? load4(o1, i, s, s1) : a0;
             const float4 c0 = NIN > 2 ? load4(o2, i, s, s2) : a0;
@@ -123,16 +125,20 @@ __global__ void __launch_bounds__(kThreads) ew_kernel(Op op, Operand o0, Operand
                 *reinterpret_cast<float4*>(out + j) = r;
             }
         }
-        // ragged tail (fewer than four elements)
-        const int64_t i = n4 + tid;
-        if (i < s.n) {
-            out[i] = op(load1(o0, i, s, s0), NIN > 1 ? load1(o1, i, s, s1) : 0.0f,
-                        NIN > 2 ? load1(o2, i, s, s2) : 0.0f);
+        // ragged tail (fewer than four elements), done by the last CTA
+        if (blockIdx.x == gridDim.x - 1) {
+            const int64_t t = n4 + threadIdx.x;
+            if (t < s.n)
+                out[t] = op(load1(o0, t, s, s0), NIN > 1 ? load1(o1, t, s, s1) : 0.0f,
+                            NIN > 2 ? load1(o2, t, s, s2) : 0.0f);
         }
     } else {
-        for (int64_t i = tid; i < s.n; i += nthreads) {
-            out[i] = op(load1(o0, i, s, s0), NIN > 1 ? load1(o1, i, s, s1) : 0.0f,
-                        NIN > 2 ? load1(o2, i, s, s2) : 0.0f);
+#pragma unroll
+        for (int u = 0; u < kPerThread; ++u) {
+            const int64_t i = base + threadIdx.x + u * kThreads;
+            if (i < s.n)
+                out[i] = op(load1(o0, i, s, s0), NIN > 1 ? load1(o1, i, s, s1) : 0.0f,
+                            NIN > 2 ? load1(o2, i, s, s2) : 0.0f);
         }
     }
 }
@@ -153,7 +159,7 @@ bool operand_vectorisable(const Operand& o, int64_t inner) {
 
 template <class Op, int NIN>
 int launch(Op op, Operand o0, Operand o1, Operand o2, float* out, int64_t n, int64_t inner, void* stream) {
-    if (n < 0 || out == nullptr && n > 0) return PAMK_ERR_ARG;
+    if (n < 0 || (out == nullptr && n > 0)) return PAMK_ERR_ARG;
     if (!operand_ok(o0) || (NIN > 1 && !operand_ok(o1)) || (NIN > 2 && !operand_ok(o2))) return PAMK_ERR_ARG;
     const bool needs_inner = o0.kind == PAMK_ROW || o0.kind == PAMK_COL ||
                              (NIN > 1 && (o1.kind == PAMK_ROW || o1.kind == PAMK_COL)) ||
@@ -164,10 +170,9 @@ int launch(Op op, Operand o0, Operand o1, Operand o2, float* out, int64_t n, int
     const bool vec = aligned16(out) && operand_vectorisable(o0, inner) &&
                      (NIN < 2 || operand_vectorisable(o1, inner)) && (NIN < 3 || operand_vectorisable(o2, inner));
     const Shape s{n, inner};
-    const int64_t per_block = (int64_t)kThreads * (vec ? 8 : 1);
-    const int64_t want = (n + per_block - 1) / per_block;
-    const int64_t cap = (int64_t)sm_count() * 8;      // 8 resident CTAs of 256 threads per SM
-    const unsigned grid = (unsigned)(want < cap ? want : cap);
+    const int64_t blocks = (n + kPerBlock - 1) / kPerBlock;
+    if (blocks > 0x7fffffff) return PAMK_ERR_SIZE;
+    const unsigned grid = (unsigned)blocks;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (vec) ew_kernel<Op, NIN, true><<<grid, kThreads, 0, st>>>(op, o0, o1, o2, out, s);
     else ew_kernel<Op, NIN, false><<<grid, kThreads, 0, st>>>(op, o0, o1, o2, out, s);

@@ -7,8 +7,9 @@
 // issue.  The algorithmic cost per multiply-accumulate is one INT32 add and one FP32 add, and the
 // kernel is organised so that the common case issues little more than those two:
 //
-//   * 128x128 output tile per CTA, 256 threads, 8x8 register micro-tile per thread: the operand
-//     fetch is four 128-bit shared-memory loads per 64 products;
+//   * 8x8 register micro-tile per thread, 128x128 (256 threads) or 64x64 (64 threads) output
+//     tile per CTA chosen per problem so that the tiles spread evenly over the 148 SMs: the
+//     operand fetch is four 128-bit shared-memory loads per 64 products;
 //   * operands are staged global -> registers -> shared one K-slab (16) ahead of the arithmetic
 //     (double-buffered shared memory, one barrier per slab); while they pass through registers
 //     the A side is pre-biased (bits - (0x3f800000 - offset)) so that the product is a single
@@ -32,8 +33,6 @@
 namespace pamk {
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 16, kThreads = 256;
-
 enum Mode { kPam = 0, kStd = 1, kBwdL = 2, kBwdR = 3 };
 
 // One matrix operand: element (r, k) of batch z lives at p[z*sb + r*sr + k*sk], where r is the
@@ -49,83 +48,102 @@ struct GemmParams {
     int64_t sDb, sDm, sDn;
     float* C;                 // [batch][M][N], or [split][batch][M][N] partials when splits > 1
     int M, N, K, batch;
-    int splits, k_chunk;      // K is cut into `splits` ranges of k_chunk (a multiple of BK)
+    int splits, k_chunk;      // K is cut into `splits` ranges of k_chunk (a multiple of the slab)
     int32_t bias_sub;         // 0x3f800000 - offset_bits
     int32_t off;              // offset_bits
 };
 
-// Shared-memory column swizzle: rows k and k+8 of a slab are offset by 16 columns so that the
-// transposing stores of a K-contiguous operand (a warp writes 16 rows x 2 k-halves) hit 32
-// distinct banks.  Groups of four columns stay contiguous for the 128-bit fragment loads.
-__device__ __forceinline__ int swz(int col, int k) { return col ^ ((k & 8) << 1); }
+// Tile shapes.  Every thread owns an 8x8 micro-tile, so a CTA has BM*BN/64 threads.
+//   128x128x16, 256 threads, 2 CTAs/SM: least staging overhead, for large outputs;
+//   64x64x8,     64 threads, 8 CTAs/SM: four times as many CTAs, for outputs that would leave a
+//                                       large tile grid with a ragged last wave (e.g. 12608 x 192).
+template <int BM_, int BN_, int BK_, int CPS_>
+struct Tile {
+    static constexpr int BM = BM_, BN = BN_, BK = BK_, kThreads = BM_ * BN_ / 64, kCtasPerSm = CPS_;
+    static constexpr int TX = BN_ / 8;
+    // float4 tasks per thread when staging one operand slab
+    static constexpr int kTasksA = BM_ * BK_ / 4 / kThreads, kTasksB = BN_ * BK_ / 4 / kThreads;
+    // rows that one warp of the K-contiguous loader covers; also the column swizzle stride
+    static constexpr int kSwz = 32 / (BK_ / 4);
+};
+using TileLarge = Tile<128, 128, 16, 2>;
+using TileSmall = Tile<64, 64, 8, 8>;
+
+// Shared-memory column swizzle: the group of four k rows f = k/4 is offset by f * kSwz columns so
+// that the transposing stores of a K-contiguous operand (a warp writes kSwz rows x BK/4 k-groups)
+// hit 32 distinct banks.  Groups of four columns stay contiguous for the 128-bit fragment loads.
+template <class T>
+__device__ __forceinline__ int swz(int col, int k) { return col ^ ((k >> 2) * T::kSwz); }
 
 // ---- loaders: global -> registers ---------------------------------------------------------------
-// KC = operand is contiguous along k (row-major A, or B given as W[N,K]): thread t takes row
-// t/2 and eight consecutive k.  Otherwise the operand is contiguous along its row index: thread t
-// takes k = t/16 and two groups of four consecutive rows, 64 apart.
+// A slab is R rows x BK k, staged as float4 "tasks"; thread t takes tasks t, t + kThreads, ...
+//   KC (operand contiguous along k: row-major A, or B given as W[N,K]):
+//       task id -> row id / (BK/4), k-group id % (BK/4): a warp reads kSwz rows x 4*BK bytes;
+//   otherwise (contiguous along the row index): task id -> k = id / (R/4), four rows (id % (R/4))*4:
+//       a warp reads 512 contiguous bytes of one k.
 // Rows beyond the matrix are clamped to the last valid row (their products land in outputs that
 // are never stored); k beyond the range reads as 0.0f, which the range rule turns into +0.
-template <bool KC, bool VEC>
-__device__ __forceinline__ void load_slab(float (&r)[8], const MatArg& m, const float* base,
+template <class T, int R, int NT, bool KC, bool VEC>
+__device__ __forceinline__ void load_slab(float (&r)[NT * 4], const MatArg& m, const float* base,
                                           int row0, int rows, int k0, int k_end, int tid) {
-    if (KC) {
-        int row = row0 + (tid >> 1);
-        row = row < rows ? row : rows - 1;
-        const int k = k0 + (tid & 1) * 8;
-        const float* src = base + (int64_t)row * m.sr + k;
-        if (VEC) {   // k_end - k0 and K are multiples of 4, pointers 16-byte aligned
-            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-            const float4 v0 = k < k_end ? __ldg(reinterpret_cast<const float4*>(src)) : z;
-            const float4 v1 = k + 4 < k_end ? __ldg(reinterpret_cast<const float4*>(src + 4)) : z;
-            r[0] = v0.x; r[1] = v0.y; r[2] = v0.z; r[3] = v0.w;
-            r[4] = v1.x; r[5] = v1.y; r[6] = v1.z; r[7] = v1.w;
-        } else {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) r[c] = k + c < k_end ? __ldg(src + c) : 0.0f;
-        }
-    } else {
-        const int k = k0 + (tid >> 4);
-        const int c0 = row0 + (tid & 15) * 4;
-        const bool live = k < k_end;
-        const float* src = base + (int64_t)k * m.sk;
-        if (VEC) {   // rows % 4 == 0: a group of four is entirely inside or entirely outside
-            const int g0 = c0 < rows ? c0 : rows - 4;
-            const int g1 = c0 + 64 < rows ? c0 + 64 : rows - 4;
-            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-            const float4 v0 = live ? __ldg(reinterpret_cast<const float4*>(src + g0)) : z;
-            const float4 v1 = live ? __ldg(reinterpret_cast<const float4*>(src + g1)) : z;
-            r[0] = v0.x; r[1] = v0.y; r[2] = v0.z; r[3] = v0.w;
-            r[4] = v1.x; r[5] = v1.y; r[6] = v1.z; r[7] = v1.w;
-        } else {
+    for (int t = 0; t < NT; ++t) {
+        const int id = tid + t * T::kThreads;
+        if (KC) {
+            int row = row0 + id / (T::BK / 4);
+            row = row < rows ? row : rows - 1;
+            const int k = k0 + (id % (T::BK / 4)) * 4;
+            const float* src = base + (int64_t)row * m.sr + k;
+            if (VEC) {   // K and the split ranges are multiples of 4, pointers 16-byte aligned
+                const float4 v = k < k_end ? __ldg(reinterpret_cast<const float4*>(src)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                r[t * 4] = v.x; r[t * 4 + 1] = v.y; r[t * 4 + 2] = v.z; r[t * 4 + 3] = v.w;
+            } else {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                int col = c0 + (c & 3) + (c >> 2) * 64;
-                col = col < rows ? col : rows - 1;
-                r[c] = live ? __ldg(src + col) : 0.0f;
+                for (int c = 0; c < 4; ++c) r[t * 4 + c] = k + c < k_end ? __ldg(src + c) : 0.0f;
+            }
+        } else {
+            const int k = k0 + id / (R / 4);
+            const int c0 = row0 + (id % (R / 4)) * 4;
+            const bool on = k < k_end;
+            const float* src = base + (int64_t)k * m.sk;
+            if (VEC) {   // rows % 4 == 0: a group of four is entirely inside or entirely outside
+                const int g = c0 < rows ? c0 : rows - 4;
+                const float4 v = on ? __ldg(reinterpret_cast<const float4*>(src + g)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                r[t * 4] = v.x; r[t * 4 + 1] = v.y; r[t * 4 + 2] = v.z; r[t * 4 + 3] = v.w;
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int col = c0 + c < rows ? c0 + c : rows - 1;
+                    r[t * 4 + c] = on ? __ldg(src + col) : 0.0f;
+                }
             }
         }
     }
 }
 
 // ---- registers -> shared, laid out [k][row] -----------------------------------------------------
-template <bool KC>
-__device__ __forceinline__ void store_slab(float* s, const float (&r)[8], int tid) {
-    if (KC) {
-        const int row = tid >> 1, kh = (tid & 1) * 8;
+template <class T, int R, int NT, bool KC>
+__device__ __forceinline__ void store_slab(float* s, const float (&r)[NT * 4], int tid) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) s[(kh + c) * BM + swz(row, kh)] = r[c];
-    } else {
-        const int k = tid >> 4, c0 = (tid & 15) * 4;
-        *reinterpret_cast<float4*>(s + k * BM + swz(c0, k)) = make_float4(r[0], r[1], r[2], r[3]);
-        *reinterpret_cast<float4*>(s + k * BM + swz(c0 + 64, k)) = make_float4(r[4], r[5], r[6], r[7]);
+    for (int t = 0; t < NT; ++t) {
+        const int id = tid + t * T::kThreads;
+        if (KC) {
+            const int row = id / (T::BK / 4), kg = (id % (T::BK / 4)) * 4;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[(kg + c) * R + swz<T>(row, kg)] = r[t * 4 + c];
+        } else {
+            const int k = id / (R / 4), c0 = (id % (R / 4)) * 4;
+            *reinterpret_cast<float4*>(s + k * R + swz<T>(c0, k)) = make_float4(r[t * 4], r[t * 4 + 1], r[t * 4 + 2], r[t * 4 + 3]);
+        }
     }
 }
 
-__device__ __forceinline__ void minmax_bits(const float (&r)[8], int& lo, int& hi) {
+template <int N>
+__device__ __forceinline__ void minmax_bits(const float (&r)[N], int& lo, int& hi) {
     lo = 0x7fffffff;
     hi = 0;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < N; ++c) {
         const int m = f2i(r[c]) & 0x7fffffff;
         lo = min(lo, m);
         hi = max(hi, m);
@@ -135,23 +153,29 @@ __device__ __forceinline__ void minmax_bits(const float (&r)[8], int& lo, int& h
 // Which loop a slab may run, from the biased-exponent ranges of its two operands.
 //   products of normal finite numbers satisfy 2^(ea+eb-254) <= |a*b| <= 2^(ea+eb-252), so
 //   ea+eb >= 132 puts every product above 1e-37 and ea+eb <= 374 keeps it below 1e37.
-enum Path { kFast = 0, kChecked = 1 };
+//   kFast:    every product in range: add the bit patterns, accumulate.
+//   kFlush:   no product can reach 1e37 and no operand is inf/NaN, but some may be tiny or zero:
+//             evaluate the true product and skip the ones that flush.
+//   kFull:    anything goes: the complete three-way rule.
+enum Path { kFast = 0, kFlush = 1, kFull = 2 };
 
 __device__ __forceinline__ int classify(int minA, int maxA, int minB, int maxB) {
     const int ea0 = minA >> 23, ea1 = maxA >> 23, eb0 = minB >> 23, eb1 = maxB >> 23;
-    const bool fast = ea0 >= 1 && eb0 >= 1 && ea1 <= 254 && eb1 <= 254 && ea0 + eb0 >= 132 && ea1 + eb1 <= 374;
-    return fast ? kFast : kChecked;
+    const bool bounded = ea1 <= 254 && eb1 <= 254 && ea1 + eb1 <= 374;
+    const bool large = ea0 >= 1 && eb0 >= 1 && ea0 + eb0 >= 132;
+    return bounded ? (large ? kFast : kFlush) : kFull;
 }
 
-template <int MODE, bool A_KC, bool B_KC, bool VEC>
-__global__ void __launch_bounds__(kThreads, MODE == kPam || MODE == kStd ? 2 : 1)
+template <int MODE, class T, bool A_KC, bool B_KC, bool VEC>
+__global__ void __launch_bounds__(T::kThreads, MODE == kPam || MODE == kStd ? T::kCtasPerSm : T::kCtasPerSm / 2)
 gemm_kernel(const GemmParams p) {
+    constexpr int BM = T::BM, BN = T::BN, BK = T::BK;
     __shared__ __align__(16) float As[2][BK * BM];
     __shared__ __align__(16) float Bs[2][BK * BN];
     __shared__ int stats[3][4];   // per slab: min/max magnitude bits of A and of B
 
     const int tid = threadIdx.x;
-    const int tx = tid & 15, ty = tid >> 4;
+    const int tx = tid % T::TX, ty = tid / T::TX;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int z = blockIdx.z / p.splits, sp = blockIdx.z - z * p.splits;
     const int k_begin = sp * p.k_chunk;
@@ -174,22 +198,24 @@ gemm_kernel(const GemmParams p) {
         const float* Db = p.D + (int64_t)z * p.sDb;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            int row = m0 + ty * 4 + (i & 3) + (i >> 2) * 64;
+            int row = m0 + ty * 4 + (i & 3) + (i >> 2) * (BM / 2);
             row = row < p.M ? row : p.M - 1;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                int col = n0 + tx * 4 + (j & 3) + (j >> 2) * 64;
+                int col = n0 + tx * 4 + (j & 3) + (j >> 2) * (BN / 2);
                 col = col < p.N ? col : p.N - 1;
                 dm[i][j] = iadd(kMant & f2i(__ldg(Db + (int64_t)row * p.sDm + (int64_t)col * p.sDn)), p.off);
             }
         }
     }
 
-    if (MODE == kPam && tid < 12) {
-        stats[tid >> 2][tid & 3] = (tid & 1) ? 0 : 0x7fffffff;   // [min, max, min, max]
-    }
+    if (MODE == kPam && tid < 12) stats[tid >> 2][tid & 3] = (tid & 1) ? 0 : 0x7fffffff;   // [min, max, min, max]
 
-    float ra[8], rb[8];
+    float ra[T::kTasksA * 4], rb[T::kTasksB * 4];
+    auto stage_load = [&](int k0) {
+        load_slab<T, BM, T::kTasksA, A_KC, VEC>(ra, p.A, Ab, m0, p.M, k0, k_end, tid);
+        load_slab<T, BN, T::kTasksB, B_KC, VEC>(rb, p.B, Bb, n0, p.N, k0, k_end, tid);
+    };
     auto stage_store = [&](int buf, int slot) {
         if (MODE == kPam) {
             int lo_a, hi_a, lo_b, hi_b;
@@ -206,16 +232,13 @@ gemm_kernel(const GemmParams p) {
                 atomicMax(&stats[slot][3], hi_b);
             }
 #pragma unroll
-            for (int c = 0; c < 8; ++c) ra[c] = i2f(isub(f2i(ra[c]), p.bias_sub));
+            for (int c = 0; c < T::kTasksA * 4; ++c) ra[c] = i2f(isub(f2i(ra[c]), p.bias_sub));
         }
-        store_slab<A_KC>(As[buf], ra, tid);
-        store_slab<B_KC>(Bs[buf], rb, tid);
+        store_slab<T, BM, T::kTasksA, A_KC>(As[buf], ra, tid);
+        store_slab<T, BN, T::kTasksB, B_KC>(Bs[buf], rb, tid);
     };
 
-    if (slabs > 0) {
-        load_slab<A_KC, VEC>(ra, p.A, Ab, m0, p.M, k_begin, k_end, tid);
-        load_slab<B_KC, VEC>(rb, p.B, Bb, n0, p.N, k_begin, k_end, tid);
-    }
+    if (slabs > 0) stage_load(k_begin);
     __syncthreads();               // stats initialised
     if (slabs > 0) stage_store(0, 0);
     __syncthreads();
@@ -223,10 +246,7 @@ gemm_kernel(const GemmParams p) {
     for (int s = 0; s < slabs; ++s) {
         const int buf = s & 1;
         const bool more = s + 1 < slabs;
-        if (more) {
-            load_slab<A_KC, VEC>(ra, p.A, Ab, m0, p.M, k_begin + (s + 1) * BK, k_end, tid);
-            load_slab<B_KC, VEC>(rb, p.B, Bb, n0, p.N, k_begin + (s + 1) * BK, k_end, tid);
-        }
+        if (more) stage_load(k_begin + (s + 1) * BK);
         int path = kFast;
         if (MODE == kPam) {
             const int slot = s % 3;
@@ -237,31 +257,43 @@ gemm_kernel(const GemmParams p) {
         const float* as = As[buf];
         const float* bs = Bs[buf];
 
-        if (MODE == kPam && path == kFast) {   // (path is kFast for the other modes, which skip this)
+#define PAMK_FRAGMENTS(kk)                                                                              \
+        const int4 a0 = *reinterpret_cast<const int4*>(as + (kk) * BM + swz<T>(ty * 4, (kk)));           \
+        const int4 a1 = *reinterpret_cast<const int4*>(as + (kk) * BM + swz<T>(ty * 4 + BM / 2, (kk)));  \
+        const int4 b0 = *reinterpret_cast<const int4*>(bs + (kk) * BN + swz<T>(tx * 4, (kk)));           \
+        const int4 b1 = *reinterpret_cast<const int4*>(bs + (kk) * BN + swz<T>(tx * 4 + BN / 2, (kk)));  \
+        const int a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};                              \
+        const int b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+
+        if (MODE == kPam && path == kFast) {
 #pragma unroll
             for (int kk = 0; kk < BK; ++kk) {
-                const int4 a0 = *reinterpret_cast<const int4*>(as + kk * BM + swz(ty * 4, kk));
-                const int4 a1 = *reinterpret_cast<const int4*>(as + kk * BM + swz(ty * 4 + 64, kk));
-                const int4 b0 = *reinterpret_cast<const int4*>(bs + kk * BN + swz(tx * 4, kk));
-                const int4 b1 = *reinterpret_cast<const int4*>(bs + kk * BN + swz(tx * 4 + 64, kk));
-                const int a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                const int b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                PAMK_FRAGMENTS(kk)
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
 #pragma unroll
                     for (int j = 0; j < 8; ++j) acc[i][j] = fadd(acc[i][j], i2f(iadd(a[i], b[j])));
             }
+        } else if (MODE == kPam && path == kFlush) {
+#pragma unroll 2
+            for (int kk = 0; kk < BK; ++kk) {
+                PAMK_FRAGMENTS(kk)
+                float araw[8];          // a[] holds pre-biased patterns; the product needs the values
+#pragma unroll
+                for (int i = 0; i < 8; ++i) araw[i] = i2f(iadd(a[i], p.bias_sub));
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float mag = fabsf(fmul(araw[i], i2f(b[j])));
+                        if (mag > i2f(kFlushBits)) acc[i][j] = fadd(acc[i][j], i2f(iadd(a[i], b[j])));
+                    }
+            }
         } else {
 #pragma unroll 2
             for (int kk = 0; kk < BK; ++kk) {
-                const int4 a0 = *reinterpret_cast<const int4*>(as + kk * BM + swz(ty * 4, kk));
-                const int4 a1 = *reinterpret_cast<const int4*>(as + kk * BM + swz(ty * 4 + 64, kk));
-                const int4 b0 = *reinterpret_cast<const int4*>(bs + kk * BN + swz(tx * 4, kk));
-                const int4 b1 = *reinterpret_cast<const int4*>(bs + kk * BN + swz(tx * 4 + 64, kk));
-                const int a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                const int b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                PAMK_FRAGMENTS(kk)
                 if constexpr (MODE == kPam) {
-                    // exact range rule on the true product; a[] holds pre-biased patterns
                     float araw[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) araw[i] = i2f(iadd(a[i], p.bias_sub));
@@ -291,6 +323,7 @@ gemm_kernel(const GemmParams p) {
                 }
             }
         }
+#undef PAMK_FRAGMENTS
 
         if (more) stage_store(buf ^ 1, (s + 1) % 3);
         __syncthreads();
@@ -301,12 +334,12 @@ gemm_kernel(const GemmParams p) {
     const bool vec_out = (p.N & 3) == 0 && aligned16(p.C);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const int row = m0 + ty * 4 + (i & 3) + (i >> 2) * 64;
+        const int row = m0 + ty * 4 + (i & 3) + (i >> 2) * (BM / 2);
         if (row >= p.M) continue;
         float* crow = Cz + (int64_t)row * p.N;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const int col = n0 + tx * 4 + h * 64;
+            const int col = n0 + tx * 4 + h * (BN / 2);
             if (vec_out) {
                 if (col < p.N)
                     *reinterpret_cast<float4*>(crow + col) =
@@ -331,9 +364,9 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     }
 }
 
-template <int MODE>
+template <int MODE, class T>
 int dispatch(const GemmParams& p, bool a_kc, bool b_kc, bool vec, dim3 grid, cudaStream_t st) {
-#define PAMK_LAUNCH(AK, BKC, V) gemm_kernel<MODE, AK, BKC, V><<<grid, kThreads, 0, st>>>(p)
+#define PAMK_LAUNCH(AK, BKC, V) gemm_kernel<MODE, T, AK, BKC, V><<<grid, T::kThreads, 0, st>>>(p)
     if (vec) {
         if (a_kc) { if (b_kc) PAMK_LAUNCH(true, true, true); else PAMK_LAUNCH(true, false, true); }
         else      { if (b_kc) PAMK_LAUNCH(false, true, true); else PAMK_LAUNCH(false, false, true); }
@@ -352,15 +385,61 @@ bool vectorisable(const MatArg& m, bool kc, int rows, int K) {
     return kc ? ((m.sr & 3) == 0 && (K & 3) == 0) : ((m.sk & 3) == 0 && (rows & 3) == 0);
 }
 
-int auto_split(int64_t batch, int64_t M, int64_t N, int64_t K) {
-    const int64_t tiles = batch * ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    const int64_t slots = (int64_t)sm_count() * 2;       // two resident CTAs per SM
-    if (tiles * 2 > slots || K < 8 * BK) return 1;         // at least half a wave already
-    int64_t s = slots / tiles;
-    const int64_t max_by_k = K / (4 * BK);                 // keep >= 4 slabs per range
-    if (s > max_by_k) s = max_by_k;
-    if (s > 64) s = 64;
-    return s < 2 ? 1 : (int)s;
+// ---- planning: tile shape and split-K ---------------------------------------------------------------
+// The kernel is issue-bound, so the time of a launch is (the largest number of tiles any SM ends up
+// with) x (work per tile), inflated when an SM holds too few warps to keep its schedulers busy.
+struct Plan {
+    bool small;      // 64x64 tiles instead of 128x128
+    int splits;
+    double cost;
+};
+
+template <class T>
+Plan plan_for(int64_t batch, int64_t M, int64_t N, int64_t K, int split_request) {
+    const int64_t sms = sm_count();
+    const int64_t tiles = batch * ((M + T::BM - 1) / T::BM) * ((N + T::BN - 1) / T::BN);
+    const int64_t slabs = (K + T::BK - 1) / T::BK;
+    int64_t s = split_request;
+    if (s == 0) {                                            // automatic
+        const int64_t slots = sms * T::kCtasPerSm;
+        s = 1;
+        if (tiles * 2 <= slots && slabs >= 8) {              // less than half a wave of tiles
+            s = slots / tiles;
+            if (s > slabs / 4) s = slabs / 4;                // keep at least four slabs per range
+            if (s > 64) s = 64;
+            if (s < 1) s = 1;
+        }
+    }
+    if (s > slabs) s = slabs;
+    const int64_t chunk_slabs = (slabs + s - 1) / s;
+    s = (slabs + chunk_slabs - 1) / chunk_slabs;             // drop ranges that would be empty
+    const int64_t ctas = tiles * s;
+    const int64_t per_sm = (ctas + sms - 1) / sms;
+    const double warps = (double)(per_sm < T::kCtasPerSm ? per_sm : T::kCtasPerSm) * (T::kThreads / 32);
+    const double util = warps >= 12.0 ? 1.0 : warps / 12.0;
+    const double staging = T::BM >= 128 ? 1.0 : 1.06;        // the small tile stages twice the bytes per MAC
+    Plan pl;
+    pl.small = T::BM < 128;
+    pl.splits = (int)s;
+    pl.cost = (double)per_sm * T::BM * T::BN * (double)(chunk_slabs * T::BK) / util * staging +
+              (s > 1 ? 2.0e6 : 0.0);                          // the reduction pass and its launch
+    return pl;
+}
+
+// 0: choose by cost; 1: always the large tile; 2: the small tile wherever it exists.
+int g_tile_policy = 0;
+
+Plan make_plan(int mode, int64_t batch, int64_t M, int64_t N, int64_t K, int split_request) {
+    const Plan large = plan_for<TileLarge>(batch, M, N, K, split_request);
+    if (mode != kPam || g_tile_policy == 1) return large;    // the other products use the large tile
+    const Plan small = plan_for<TileSmall>(batch, M, N, K, split_request);
+    if (g_tile_policy == 2) return small;
+    return small.cost < large.cost ? small : large;
+}
+
+bool workspace_ok(const void* ws, size_t bytes, int splits, int64_t count) {
+    return ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255u) == 0 &&
+           bytes >= (size_t)splits * (size_t)count * sizeof(float);
 }
 
 int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspace, size_t workspace_bytes,
@@ -371,46 +450,39 @@ int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspa
         const cudaError_t e = cudaMemsetAsync(p.C, 0, count * sizeof(float), st);
         return e == cudaSuccess ? PAMK_OK : record_cuda_error(e);
     }
-    int splits = split_k;
-    if (splits == 0) {
-        splits = auto_split(p.batch, p.M, p.N, p.K);
-        if (splits > 1 && (workspace == nullptr || workspace_bytes < (size_t)splits * count * sizeof(float) ||
-                           (reinterpret_cast<uintptr_t>(workspace) & 255u)))
-            splits = 1;
+    if (split_k < 0) return PAMK_ERR_ARG;
+    Plan pl = make_plan(mode, p.batch, p.M, p.N, p.K, split_k);
+    if (pl.splits > 1 && !workspace_ok(workspace, workspace_bytes, pl.splits, count)) {
+        if (split_k != 0) return PAMK_ERR_WORKSPACE;         // an explicit split needs its scratch
+        pl = make_plan(mode, p.batch, p.M, p.N, p.K, 1);     // automatic: fall back to no split
     }
-    if (splits < 1) return PAMK_ERR_ARG;
-    const int slabs_total = (p.K + BK - 1) / BK;
-    if (splits > slabs_total) splits = slabs_total;
+    const int bm = pl.small ? TileSmall::BM : TileLarge::BM, bn = pl.small ? TileSmall::BN : TileLarge::BN;
+    const int bk = pl.small ? TileSmall::BK : TileLarge::BK;
     float* out = p.C;
-    if (splits > 1) {
-        if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255u) ||
-            workspace_bytes < (size_t)splits * count * sizeof(float))
-            return PAMK_ERR_WORKSPACE;
-        p.C = static_cast<float*>(workspace);
-    }
-    p.splits = splits;
-    p.k_chunk = ((slabs_total + splits - 1) / splits) * BK;
-    // ranges that would start beyond K are dropped (can happen after rounding k_chunk up)
-    while (p.splits > 1 && (int64_t)(p.splits - 1) * p.k_chunk >= p.K) --p.splits;
-    splits = p.splits;
-    if (splits == 1) p.C = out;
+    if (pl.splits > 1) p.C = static_cast<float*>(workspace);
+    const int slabs_total = (p.K + bk - 1) / bk;
+    p.splits = pl.splits;
+    p.k_chunk = ((slabs_total + pl.splits - 1) / pl.splits) * bk;
 
-    const int64_t gx = (p.N + BN - 1) / BN, gy = (p.M + BM - 1) / BM, gz = (int64_t)p.batch * splits;
+    const int64_t gx = (p.N + bn - 1) / bn, gy = (p.M + bm - 1) / bm, gz = (int64_t)p.batch * pl.splits;
     if (gy > 65535 || gz > 65535) return PAMK_ERR_SIZE;
     const dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)gz);
     const bool vec = vectorisable(p.A, a_kc, p.M, p.K) && vectorisable(p.B, b_kc, p.N, p.K);
     int rc;
     switch (mode) {
-        case kPam: rc = dispatch<kPam>(p, a_kc, b_kc, vec, grid, st); break;
-        case kStd: rc = dispatch<kStd>(p, a_kc, b_kc, vec, grid, st); break;
-        case kBwdL: rc = dispatch<kBwdL>(p, a_kc, b_kc, vec, grid, st); break;
-        default: rc = dispatch<kBwdR>(p, a_kc, b_kc, vec, grid, st); break;
+        case kPam:
+            rc = pl.small ? dispatch<kPam, TileSmall>(p, a_kc, b_kc, vec, grid, st)
+                          : dispatch<kPam, TileLarge>(p, a_kc, b_kc, vec, grid, st);
+            break;
+        case kStd: rc = dispatch<kStd, TileLarge>(p, a_kc, b_kc, vec, grid, st); break;
+        case kBwdL: rc = dispatch<kBwdL, TileLarge>(p, a_kc, b_kc, vec, grid, st); break;
+        default: rc = dispatch<kBwdR, TileLarge>(p, a_kc, b_kc, vec, grid, st); break;
     }
-    if (rc != PAMK_OK || splits == 1) return rc;
+    if (rc != PAMK_OK || pl.splits == 1) return rc;
     const int64_t blocks = (count + 255) / 256;
     const int64_t cap = (int64_t)sm_count() * 8;
     splitk_reduce_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, st>>>(
-        static_cast<const float*>(workspace), out, count, splits);
+        static_cast<const float*>(workspace), out, count, pl.splits);
     return check_launch();
 }
 
@@ -439,9 +511,15 @@ size_t pamk_matmul_workspace_bytes(int64_t batch, int64_t M, int64_t N, int spli
     return (size_t)split_k * (size_t)batch * (size_t)M * (size_t)N * sizeof(float);
 }
 
+int pamk_matmul_set_tile_policy(int policy) {
+    if (policy < 0 || policy > 2) return PAMK_ERR_ARG;
+    g_tile_policy = policy;
+    return PAMK_OK;
+}
+
 int pamk_matmul_auto_split(int64_t batch, int64_t M, int64_t N, int64_t K) {
     if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 1;
-    return auto_split(batch, M, N, K);
+    return make_plan(kPam, batch, M, N, K, 0).splits;
 }
 
 int pamk_matmul(int mul_kind, const float* A, const float* B, float* C,

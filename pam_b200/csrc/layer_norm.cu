@@ -1,0 +1,332 @@
+// pam_ln: fused PAM layer normalisation, forward and backward.
+//
+// The reference evaluates layer_norm as a chain of about 15 elementwise launches forward and 40
+// backward (epfml/pam pam/pam_ops.py:350-378 through autograd), each a full read and write of the
+// activation, with every intermediate rounded to fp32.  Here one warp owns a row: the row stays
+// in registers, the two (forward) or four (backward) row sums are warp-shuffle reductions, and
+// every primitive of the chain is evaluated by the same scalar function the elementwise kernels
+// use, rounding where the reference rounds.  Traffic is the algorithmic minimum: read x, write y
+// (8 B/element) forward; read x and dy, write dx (12 B/element) backward.
+//
+// The chain, per row of width n (nf = float(n), "op" = PAM primitive, +,- = ordinary fp32):
+//   mu = pad(sum x, nf);  c = x - mu;  var = pad(sum pam(c, c), nf);  v = var + eps
+//   denom = (v == 0) ? 0 : exp2_op(pam(log2_op(v), 0.5))          [pam_ops.pow, :70-79]
+//   y = pam(pad(c, denom), w) + b
+// The backward pass recomputes the forward chain from x and applies, primitive by primitive, the
+// gradient pairing of pam/cuda_bindings.py (approximate: gradients are PAM products with the
+// other operand; exact: the piecewise-affine slopes).
+#include "common.cuh"
+#include "pam_scalar.cuh"
+
+namespace pamk {
+namespace {
+
+constexpr int kWarpsPerCta = 4;
+constexpr int kThreads = kWarpsPerCta * 32;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v = fadd(v, __shfl_xor_sync(0xffffffffu, v, d));
+    return v;
+}
+
+struct LnArgs {
+    const float* x;
+    const float* w;      // may be null
+    const float* b;      // may be null
+    const float* dy;     // backward only
+    float* out;          // y (forward) or dx (backward)
+    float* partials;     // backward with w/b: [gridDim.x][2][width] per-CTA sums for dw, db
+    int64_t rows;
+    int width;
+    float nf, eps;
+    int32_t off;
+};
+
+// Row-level scalars of the forward chain.
+struct RowStats {
+    float s1, mu, s2, v, l, m, e, denom;
+};
+
+__device__ __forceinline__ void finish_stats(RowStats& r, const LnArgs& a) {
+    const float lb2 = log2f(2.0f);                 // the base-2 kernels scale by log2f(2) = 1
+    const float var = div(r.s2, a.nf, a.off);
+    r.v = fadd(var, a.eps);
+    r.l = log_base(r.v, lb2, a.off);
+    r.m = mul(r.l, 0.5f, a.off);
+    r.e = exp_base(r.m, lb2, a.off);
+    r.denom = r.v == 0.0f ? 0.0f : r.e;
+}
+
+// A lane holds NCH chunks of VEC consecutive columns: chunk q of lane L starts at column
+// (q * 32 + L) * VEC.  With VEC = 4 every access of a warp is a contiguous 512-byte run.
+template <int VEC, int NCH>
+struct RowRegs {
+    float v[NCH * VEC];
+};
+
+template <int VEC, int NCH>
+__device__ __forceinline__ void load_row(RowRegs<VEC, NCH>& r, const float* p, int width, int lane, float fill) {
+#pragma unroll
+    for (int q = 0; q < NCH; ++q) {
+        const int col = (q * 32 + lane) * VEC;
+        if (VEC == 4) {
+            if (col < width) {
+                const float4 t = __ldg(reinterpret_cast<const float4*>(p + col));
+                r.v[q * 4] = t.x; r.v[q * 4 + 1] = t.y; r.v[q * 4 + 2] = t.z; r.v[q * 4 + 3] = t.w;
+            } else {
+                r.v[q * 4] = r.v[q * 4 + 1] = r.v[q * 4 + 2] = r.v[q * 4 + 3] = fill;
+            }
+        } else {
+            r.v[q] = col < width ? __ldg(p + col) : fill;
+        }
+    }
+}
+
+template <int VEC, int NCH>
+__device__ __forceinline__ void store_row(const RowRegs<VEC, NCH>& r, float* p, int width, int lane) {
+#pragma unroll
+    for (int q = 0; q < NCH; ++q) {
+        const int col = (q * 32 + lane) * VEC;
+        if (col < width) {
+            if (VEC == 4)
+                *reinterpret_cast<float4*>(p + col) = make_float4(r.v[q * 4], r.v[q * 4 + 1], r.v[q * 4 + 2], r.v[q * 4 + 3]);
+            else
+                p[col] = r.v[q];
+        }
+    }
+}
+
+template <int VEC, int NCH>
+__device__ __forceinline__ bool live(int i, int width, int lane) {
+    return ((i / VEC) * 32 + lane) * VEC + (i % VEC) < width;
+}
+
+// Forward chain up to the centred row and the row scalars.  Padding lanes hold 0 in `c` so that
+// pam(0, 0) = +0 leaves the sums untouched.
+template <int VEC, int NCH>
+__device__ __forceinline__ void centre_and_stats(RowRegs<VEC, NCH>& c, RowStats& st, const LnArgs& a, int lane) {
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NCH * VEC; ++i) s = fadd(s, c.v[i]);
+    st.s1 = warp_sum(s);
+    st.mu = div(st.s1, a.nf, a.off);
+    s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NCH * VEC; ++i) {
+        c.v[i] = live<VEC, NCH>(i, a.width, lane) ? fadd(c.v[i], -st.mu) : 0.0f;
+        s = fadd(s, mul(c.v[i], c.v[i], a.off));
+    }
+    st.s2 = warp_sum(s);
+    finish_stats(st, a);
+}
+
+template <int VEC, int NCH>
+__global__ void __launch_bounds__(kThreads) ln_fwd_kernel(const LnArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
+    RowRegs<VEC, NCH> w, b;
+    if (a.w) load_row<VEC, NCH>(w, a.w, a.width, lane, 1.0f);
+    if (a.b) load_row<VEC, NCH>(b, a.b, a.width, lane, 0.0f);
+    for (int64_t row = warp; row < a.rows; row += nwarps) {
+        RowRegs<VEC, NCH> c;
+        load_row<VEC, NCH>(c, a.x + row * a.width, a.width, lane, 0.0f);
+        RowStats st;
+        centre_and_stats<VEC, NCH>(c, st, a, lane);
+#pragma unroll
+        for (int i = 0; i < NCH * VEC; ++i) {
+            float y = div(c.v[i], st.denom, a.off);
+            if (a.w) y = mul(y, w.v[i], a.off);
+            if (a.b) y = fadd(y, b.v[i]);
+            c.v[i] = y;
+        }
+        store_row<VEC, NCH>(c, a.out + row * a.width, a.width, lane);
+    }
+}
+
+template <int VEC, int NCH, bool APPROX>
+__global__ void __launch_bounds__(kThreads) ln_bwd_kernel(const LnArgs a) {
+    __shared__ float stage[kWarpsPerCta][NCH * VEC][32];
+    const int lane = threadIdx.x & 31;
+    const int wid = threadIdx.x >> 5;
+    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + wid;
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
+    const float ln2 = 0.693147180559945309417f;      // float(math.log(2.0)), cuda_bindings.py:232,271
+    const float recip_n = div(1.0f, a.nf, a.off);
+    RowRegs<VEC, NCH> w, dw, db;
+    if (a.w) load_row<VEC, NCH>(w, a.w, a.width, lane, 1.0f);
+#pragma unroll
+    for (int i = 0; i < NCH * VEC; ++i) dw.v[i] = db.v[i] = 0.0f;
+
+    for (int64_t row = warp; row < a.rows; row += nwarps) {
+        RowRegs<VEC, NCH> c, g;
+        load_row<VEC, NCH>(c, a.x + row * a.width, a.width, lane, 0.0f);
+        load_row<VEC, NCH>(g, a.dy + row * a.width, a.width, lane, 0.0f);
+        RowStats st;
+        centre_and_stats<VEC, NCH>(c, st, a, lane);
+        const float recip = div(1.0f, st.denom, a.off);
+
+        // d(out)/d(xn), the division's two gradients; g is overwritten by d_c1
+        float sum_dden = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NCH * VEC; ++i) {
+            const bool on = live<VEC, NCH>(i, a.width, lane);
+            const float xn = div(c.v[i], st.denom, a.off);
+            float dxn = g.v[i];
+            if (a.w) {
+                if (on) {
+                    dw.v[i] = fadd(dw.v[i], APPROX ? mul(g.v[i], xn, a.off) : mul_bwd(w.v[i], xn, g.v[i], a.off));
+                    db.v[i] = fadd(db.v[i], g.v[i]);
+                }
+                dxn = APPROX ? mul(g.v[i], w.v[i], a.off) : mul_bwd(xn, w.v[i], g.v[i], a.off);
+            } else if (a.partials && on) {
+                db.v[i] = fadd(db.v[i], g.v[i]);
+            }
+            const float dden = APPROX ? -mul(div(xn, st.denom, a.off), dxn, a.off)
+                                      : div_bwd(c.v[i], st.denom, dxn, a.off);
+            if (on) sum_dden = fadd(sum_dden, dden);
+            g.v[i] = APPROX ? mul(recip, dxn, a.off) : mul_bwd(c.v[i], recip, dxn, 0);
+        }
+        const float d_denom = warp_sum(sum_dden);
+
+        // scalar chain back through pow(v, 0.5) and the variance
+        const float lb2 = log2f(2.0f);
+        const float d_e = st.v == 0.0f ? 0.0f : d_denom;
+        const float d_m = APPROX ? mul(mul(st.e, ln2, a.off), d_e, a.off) : exp_base_bwd(st.m, d_e, lb2, a.off);
+        const float d_l = APPROX ? mul(d_m, 0.5f, a.off) : mul_bwd(st.l, 0.5f, d_m, a.off);
+        const float d_v = APPROX ? div(div(d_l, st.v, a.off), ln2, a.off) : log_base_bwd(st.v, d_l, lb2, a.off);
+        const float d_s2 = APPROX ? mul(recip_n, d_v, a.off) : mul_bwd(st.s2, recip_n, d_v, 0);
+
+        // c feeds the division and both operands of pam(c, c)
+        float sum_dc = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NCH * VEC; ++i) {
+            const float dsq = APPROX ? mul(d_s2, c.v[i], a.off) : mul_bwd(c.v[i], c.v[i], d_s2, a.off);
+            g.v[i] = fadd(fadd(g.v[i], dsq), dsq);
+            if (live<VEC, NCH>(i, a.width, lane)) sum_dc = fadd(sum_dc, g.v[i]);
+        }
+        const float d_mu = -warp_sum(sum_dc);
+        const float d_s1 = APPROX ? mul(recip_n, d_mu, a.off) : mul_bwd(st.s1, recip_n, d_mu, 0);
+#pragma unroll
+        for (int i = 0; i < NCH * VEC; ++i) g.v[i] = fadd(g.v[i], d_s1);
+        store_row<VEC, NCH>(g, a.out + row * a.width, a.width, lane);
+    }
+
+    // per-CTA column sums for dw / db: warps are added in warp order, CTAs by the second kernel
+    if (a.partials) {
+        float* slot = a.partials + (int64_t)blockIdx.x * 2 * a.width;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) stage[wid][i][lane] = which == 0 ? dw.v[i] : db.v[i];
+            __syncthreads();
+            if (wid == 0) {
+#pragma unroll
+                for (int i = 0; i < NCH * VEC; ++i) {
+                    const int col = ((i / VEC) * 32 + lane) * VEC + (i % VEC);
+                    float t = stage[0][i][lane];
+#pragma unroll
+                    for (int k = 1; k < kWarpsPerCta; ++k) t = fadd(t, stage[k][i][lane]);
+                    if (col < a.width) slot[which * a.width + col] = t;
+                }
+            }
+        }
+    }
+}
+
+// dw[c] = sum over CTAs of partials[cta][0][c], db likewise, in CTA order.
+__global__ void ln_param_grad_kernel(const float* __restrict__ partials, float* __restrict__ dw,
+                                     float* __restrict__ db, int ctas, int width) {
+    const int col = blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= width) return;
+    float sw = 0.0f, sb = 0.0f;
+    for (int k = 0; k < ctas; ++k) {
+        sw = fadd(sw, partials[((int64_t)k * 2) * width + col]);
+        sb = fadd(sb, partials[((int64_t)k * 2 + 1) * width + col]);
+    }
+    if (dw) dw[col] = sw;
+    if (db) db[col] = sb;
+}
+
+int pick_grid(int64_t rows) {
+    const int64_t want = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
+    const int64_t cap = (int64_t)sm_count() * 16;            // 16 CTAs x 4 warps: 64 warps per SM
+    return (int)(want < cap ? want : cap);
+}
+
+template <bool BWD, bool APPROX>
+int launch(const LnArgs& a, int grid, cudaStream_t st) {
+    const bool vec = (a.width & 3) == 0 && aligned16(a.x) && aligned16(a.out) && (!a.w || aligned16(a.w)) &&
+                     (!a.b || aligned16(a.b)) && (!a.dy || aligned16(a.dy));
+#define PAMK_LN(V, N)                                                                   \
+    do {                                                                                \
+        if (BWD) ln_bwd_kernel<V, N, APPROX><<<grid, kThreads, 0, st>>>(a);             \
+        else ln_fwd_kernel<V, N><<<grid, kThreads, 0, st>>>(a);                         \
+        return check_launch();                                                          \
+    } while (0)
+    if (vec) {
+        if (a.width <= 256) PAMK_LN(4, 2);
+        if (a.width <= 512) PAMK_LN(4, 4);
+        if (a.width <= 1024) PAMK_LN(4, 8);
+    } else {
+        if (a.width <= 256) PAMK_LN(1, 8);
+        if (a.width <= 1024) PAMK_LN(1, 32);
+    }
+#undef PAMK_LN
+    return PAMK_ERR_SIZE;
+}
+
+}  // namespace
+}  // namespace pamk
+
+using namespace pamk;
+
+extern "C" {
+
+int pamk_layer_norm_max_width(void) { return 1024; }
+
+int pamk_layer_norm_fwd(const float* x, const float* weight, const float* bias, float* y,
+                        int64_t rows, int64_t width, float eps, float offset, void* stream) {
+    if (rows < 0 || width <= 0) return PAMK_ERR_ARG;
+    if (width > 1024) return PAMK_ERR_SIZE;
+    if (rows == 0) return PAMK_OK;
+    if (!x || !y) return PAMK_ERR_ARG;
+    LnArgs a{x, weight, bias, nullptr, y, nullptr, rows, (int)width, (float)width, eps, offset_bits(offset)};
+    return launch<false, false>(a, pick_grid(rows), static_cast<cudaStream_t>(stream));
+}
+
+size_t pamk_layer_norm_bwd_workspace_bytes(int64_t rows, int64_t width) {
+    if (rows <= 0 || width <= 0) return 0;
+    return (size_t)pick_grid(rows) * 2 * (size_t)width * sizeof(float);
+}
+
+int pamk_layer_norm_bwd(const float* x, const float* weight, const float* dy, float* dx,
+                        float* dweight, float* dbias, int64_t rows, int64_t width, float eps, float offset,
+                        int approx_bwd, void* workspace, size_t workspace_bytes, void* stream) {
+    if (rows < 0 || width <= 0) return PAMK_ERR_ARG;
+    if (width > 1024) return PAMK_ERR_SIZE;
+    if (dweight && !weight) return PAMK_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (rows == 0) {
+        if (dweight) cudaMemsetAsync(dweight, 0, width * sizeof(float), st);
+        if (dbias) cudaMemsetAsync(dbias, 0, width * sizeof(float), st);
+        return PAMK_OK;
+    }
+    if (!x || !dy || !dx) return PAMK_ERR_ARG;
+    const int grid = pick_grid(rows);
+    const bool params = dweight || dbias;
+    if (params && (!workspace || workspace_bytes < pamk_layer_norm_bwd_workspace_bytes(rows, width) ||
+                   (reinterpret_cast<uintptr_t>(workspace) & 15u)))
+        return PAMK_ERR_WORKSPACE;
+    LnArgs a{x, weight, nullptr, dy, dx, params ? static_cast<float*>(workspace) : nullptr,
+             rows, (int)width, (float)width, eps, offset_bits(offset)};
+    const int rc = approx_bwd ? launch<true, true>(a, grid, st) : launch<true, false>(a, grid, st);
+    if (rc != PAMK_OK || !params) return rc;
+    ln_param_grad_kernel<<<(unsigned)((width + 127) / 128), 128, 0, st>>>(static_cast<const float*>(workspace), dweight,
+                                                                         dbias, grid, (int)width);
+    return check_launch();
+}
+
+}

@@ -35,7 +35,9 @@ PAM_HD float i2f(int32_t i) { return __int_as_float(i); }
 PAM_HD float fmul(float a, float b) { return __fmul_rn(a, b); }   // never contracted into an FMA
 PAM_HD float fadd(float a, float b) { return __fadd_rn(a, b); }
 PAM_HD float fdiv(float a, float b) { return __fdiv_rn(a, b); }
-PAM_HD float quiet_nan() { return __int_as_float(0x7fffffff); }
+// The reference returns the NAN macro, which nvcc folds to 0x7fc00000 in device code too.  The
+// payload matters: a later pam_bwd may do integer arithmetic on these bits.
+PAM_HD float quiet_nan() { return __int_as_float(0x7fc00000); }
 #else
 PAM_HD int32_t f2i(float x) { int32_t i; __builtin_memcpy(&i, &x, 4); return i; }
 PAM_HD float i2f(int32_t i) { float x; __builtin_memcpy(&x, &i, 4); return x; }

@@ -3,17 +3,106 @@
 Each fused op computes exactly the chain of PAM primitives that the reference runs as separate
 launches from Python, rounding at the same points, in one pass over the data.  ``*_supported``
 tells the operator library whether a call can take the fused route; otherwise it composes the
-primitives one kernel at a time.
+primitives one kernel at a time (still on the GPU).
 """
+import math
 
+import torch
+
+from . import _lib
+
+# Set to False to force the one-kernel-per-primitive composition everywhere (used by tests to
+# compare the two routes).
+enabled = True
+
+
+def _offset(offset):
+    return 1.0 if offset is None else float(offset)
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+def _workspace(device, nbytes):
+    from .cuda_bindings import _workspace as ws
+    return ws(device, nbytes)
+
+
+# ---- layer normalisation -------------------------------------------------------------------------
+
+def _uniform(approx_bwd):
+    """The fused kernels take one approx_bwd flag; a (first, second) pair must agree."""
+    return isinstance(approx_bwd, bool) or len(set(approx_bwd)) == 1
+
+
+def layer_norm_supported(x, normalized_shape, weight, bias, approx_bwd=False):
+    if not (enabled and isinstance(x, torch.Tensor) and x.is_cuda and x.dtype == torch.float32):
+        return False
+    if not _uniform(approx_bwd):
+        return False
+    width = math.prod(normalized_shape)
+    if width > 1024 or x.numel() == 0:
+        return False
+    for p in (weight, bias):
+        if p is not None and not (p.is_cuda and p.dtype == torch.float32 and p.numel() == width):
+            return False
+    return True
+
+
+class _LayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, width, eps, offset, approx):
+        rows2d = x.reshape(-1, width).contiguous()
+        w = weight.contiguous().view(-1) if weight is not None else None
+        b = bias.contiguous().view(-1) if bias is not None else None
+        y = torch.empty_like(rows2d)
+        dev = x.device
+        with _lib.device_guard(dev):
+            status = _lib.lib().pamk_layer_norm_fwd(rows2d.data_ptr(), _ptr(w), _ptr(b), y.data_ptr(),
+                                                    rows2d.shape[0], width, eps, offset, _lib.stream_ptr(dev))
+        _lib.check(status, "pamk_layer_norm_fwd")
+        ctx.save_for_backward(rows2d, w)
+        ctx.cfg = (width, eps, offset, approx, bias is not None, x.shape,
+                   weight.shape if weight is not None else None, bias.shape if bias is not None else None)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        rows2d, w = ctx.saved_tensors
+        width, eps, offset, approx, has_bias, x_shape, w_shape, b_shape = ctx.cfg
+        dev = rows2d.device
+        g2 = g.reshape(-1, width).contiguous()
+        dx = torch.empty_like(rows2d)
+        need_w = w is not None and ctx.needs_input_grad[1]
+        need_b = has_bias and ctx.needs_input_grad[2]
+        dw = torch.empty(width, dtype=torch.float32, device=dev) if need_w else None
+        db = torch.empty(width, dtype=torch.float32, device=dev) if need_b else None
+        handle = _lib.lib()
+        ws_bytes = handle.pamk_layer_norm_bwd_workspace_bytes(rows2d.shape[0], width) if (need_w or need_b) else 0
+        ws = _workspace(dev, ws_bytes) if ws_bytes else None
+        with _lib.device_guard(dev):
+            status = handle.pamk_layer_norm_bwd(rows2d.data_ptr(), _ptr(w), g2.data_ptr(), dx.data_ptr(), _ptr(dw),
+                                                _ptr(db), rows2d.shape[0], width, eps, offset, int(bool(approx)),
+                                                _ptr(ws), ws_bytes, _lib.stream_ptr(dev))
+        _lib.check(status, "pamk_layer_norm_bwd")
+        return (dx.view(x_shape), dw.view(w_shape) if need_w else None, db.view(b_shape) if need_b else None,
+                None, None, None, None)
+
+
+def layer_norm(x, normalized_shape, weight, bias, eps, *, offset=None, approx_bwd=False):
+    if not isinstance(approx_bwd, bool):
+        approx_bwd = bool(approx_bwd[0])
+    return _LayerNorm.apply(x, weight, bias, math.prod(normalized_shape), float(eps), _offset(offset), approx_bwd)
+
+
+# ---- softmax ---------------------------------------------------------------------------------------
 
 def softmax_supported(x, dim):
     return False
 
 
-def layer_norm_supported(x, normalized_shape, weight, bias):
-    return False
-
+# ---- Adam --------------------------------------------------------------------------------------------
 
 def adam_supported(p, grad):
     return False

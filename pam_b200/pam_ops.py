@@ -245,7 +245,7 @@ def layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-05, *,
         normalized_shape = (normalized_shape,)
     normalized_shape = tuple(normalized_shape)
     assert tuple(x.shape[-len(normalized_shape):]) == normalized_shape
-    if fused.layer_norm_supported(x, normalized_shape, weight, bias):
+    if fused.layer_norm_supported(x, normalized_shape, weight, bias, approx_bwd):
         return fused.layer_norm(x, normalized_shape, weight, bias, eps, offset=offset, approx_bwd=approx_bwd)
     kw = dict(offset=offset, approx_bwd=approx_bwd)
     rows = x.reshape(-1, math.prod(normalized_shape))

@@ -27,9 +27,27 @@ def dev():
     return torch.device("cuda", 0)
 
 
+@pytest.fixture(autouse=True)
+def strict_order(pam):
+    """Matrix products are compared bit for bit, so K is never split here (the split-K test
+    passes its split explicitly)."""
+    pam.set_strict_k_order(True)
+    yield
+    pam.set_strict_k_order(False)
+
+
 @pytest.fixture(scope="module")
 def K(oracle):
     return oracle.kernels()
+
+
+@pytest.fixture(params=[1, 2], ids=["tile128", "tile64"])
+def tile(request, pam):
+    """Runs a matrix-product test once per CTA tile shape (the library picks one per problem)."""
+    from pam_b200 import _lib
+    _lib.check(_lib.lib().pamk_matmul_set_tile_policy(request.param), "tile policy")
+    yield request.param
+    _lib.lib().pamk_matmul_set_tile_policy(0)
 
 
 SPECIALS = [0.0, -0.0, 1e-40, -1e-40, 1.4e-45, -1.4e-45, 1e30, -1e30, 1e-30, -1e-30]
@@ -228,7 +246,7 @@ def _layouts(A, B):
 
 
 @pytest.mark.parametrize("M,N,Kdim", SHAPES)
-def test_matmul_shapes_layouts_bit_exact(pam, K, dev, M, N, Kdim):
+def test_matmul_shapes_layouts_bit_exact(pam, K, dev, tile, M, N, Kdim):
     g = torch.Generator().manual_seed(M * 1000 + N)
     A, B = torch.randn(M, Kdim, generator=g), torch.randn(Kdim, N, generator=g) * 0.02
     want = K.pam_matmul_fwd(A, B)
@@ -247,7 +265,7 @@ def test_matmul_shapes_layouts_bit_exact(pam, K, dev, M, N, Kdim):
 
 @pytest.mark.parametrize("frac", [0.01, 0.3])
 @pytest.mark.parametrize("offset", [1.0, 1.0552])
-def test_matmul_special_values_bit_exact(pam, K, dev, frac, offset):
+def test_matmul_special_values_bit_exact(pam, K, dev, tile, frac, offset):
     """Zeros, denormals, +-1e30 / +-1e-30, inf and NaN in the operands: the hoisted range rule must
     reproduce flush-to-+0, NaN-on-overflow and raw-bit denormal products exactly."""
     g = torch.Generator().manual_seed(int(frac * 100))
@@ -262,7 +280,7 @@ def test_matmul_special_values_bit_exact(pam, K, dev, frac, offset):
         assert_bits_equal(pam.cuda_bindings.cuda_kernels.pam_matmul_fwd(a, b, True, True, offset), want, name)
 
 
-def test_matmul_tiny_and_huge_magnitudes(pam, K, dev):
+def test_matmul_tiny_and_huge_magnitudes(pam, K, dev, tile):
     """Operands whose exponent ranges make the per-slab classification take each branch: all
     products far in range, products straddling the 1e-37 flush threshold, and straddling 1e37."""
     g = torch.Generator().manual_seed(3)
@@ -274,7 +292,7 @@ def test_matmul_tiny_and_huge_magnitudes(pam, K, dev):
         assert_bits_equal(got, want, f"scales {scale_a} x {scale_b}")
 
 
-def test_bmm_bit_exact_and_guard_bands(pam, K, dev):
+def test_bmm_bit_exact_and_guard_bands(pam, K, dev, tile):
     from pam_b200 import _lib
     g = torch.Generator().manual_seed(8)
     A, B = torch.randn(11, 13, 15, generator=g), torch.randn(11, 15, 19, generator=g)
@@ -304,7 +322,7 @@ def _sum_abs_products(K, A, B):
 
 
 @pytest.mark.parametrize("split", [2, 5, 16])
-def test_matmul_split_k_within_tolerance(pam, K, dev, split):
+def test_matmul_split_k_within_tolerance(pam, K, dev, tile, split):
     """Split-K adds the same bit-exact products in a different association.  Bound for any
     order: |C - S| <= 2 * K * 2^-24 * sum|p_k|  (S the exact sum of the products)."""
     from pam_b200 import cuda_bindings as cb
@@ -327,13 +345,9 @@ def test_config1_matmul_forward_and_approx_backward(pam, K, dev):
     N(0,1) grad_out; per-product results on a sampled block and all three products bit-exact."""
     g = torch.Generator().manual_seed(1)
     A, B, G = torch.randn(512, 1024, generator=g), torch.randn(1024, 512, generator=g), torch.randn(512, 512, generator=g)
-    pam.set_strict_k_order(True)
-    try:
-        Ad, Bd = A.to(dev).requires_grad_(), B.to(dev).requires_grad_()
-        C = pam.matmul(Ad, Bd, approx_bwd=True)
-        C.backward(G.to(dev))
-    finally:
-        pam.set_strict_k_order(False)
+    Ad, Bd = A.to(dev).requires_grad_(), B.to(dev).requires_grad_()
+    C = pam.matmul(Ad, Bd, approx_bwd=True)
+    C.backward(G.to(dev))
     assert_bits_equal(C, K.pam_matmul_fwd(A, B), "C")
     assert_bits_equal(Ad.grad, K.pam_matmul_fwd(G, B.T), "dA")
     assert_bits_equal(Bd.grad, K.pam_matmul_fwd(A.T, G), "dB")
@@ -343,28 +357,24 @@ def test_config1_matmul_forward_and_approx_backward(pam, K, dev):
     assert_bits_equal(prod, want, "per-product")
 
 
-def test_deit_linear_set_bit_exact_on_row_sample(pam, K, dev):
+def test_deit_linear_set_bit_exact_on_row_sample(pam, K, dev, tile):
     """BASELINE config 2 shapes (M = 12608 tokens, 192->576, 192->192, 192->768, 768->192,
     trunc-normal(0.02) weights): full-size products on the GPU, checked bit for bit on a sample of
     rows against the oracle, forward and both approx_bwd gradients."""
     g = torch.Generator().manual_seed(2)
     M = 12608
     rows = torch.randperm(M, generator=g)[:96]
-    pam.set_strict_k_order(True)
-    try:
-        for k_in, n_out in ((192, 576), (192, 192), (192, 768), (768, 192)):
-            X = torch.randn(M, k_in, generator=g)
-            W = torch.nn.init.trunc_normal_(torch.empty(n_out, k_in), std=0.02, generator=g)
-            G = torch.randn(M, n_out, generator=g)
-            Xd, Wd = X.to(dev).requires_grad_(), W.to(dev).requires_grad_()
-            Y = pam.linear(Xd, Wd, approx_bwd=True)
-            Y.backward(G.to(dev))
-            assert_bits_equal(Y[rows.to(dev)], K.pam_matmul_fwd(X[rows], W.T), f"Y {k_in}->{n_out}")
-            assert_bits_equal(Xd.grad[rows.to(dev)], K.pam_matmul_fwd(G[rows], W), f"dX {k_in}->{n_out}")
-            cols = torch.arange(0, k_in, 7)
-            assert_bits_equal(Wd.grad[:, cols.to(dev)], K.pam_matmul_fwd(G.T, X[:, cols]), f"dW {k_in}->{n_out}")
-    finally:
-        pam.set_strict_k_order(False)
+    for k_in, n_out in ((192, 576), (192, 192), (192, 768), (768, 192)):
+        X = torch.randn(M, k_in, generator=g)
+        W = torch.nn.init.trunc_normal_(torch.empty(n_out, k_in), std=0.02, generator=g)
+        G = torch.randn(M, n_out, generator=g)
+        Xd, Wd = X.to(dev).requires_grad_(), W.to(dev).requires_grad_()
+        Y = pam.linear(Xd, Wd, approx_bwd=True)
+        Y.backward(G.to(dev))
+        assert_bits_equal(Y[rows.to(dev)], K.pam_matmul_fwd(X[rows], W.T), f"Y {k_in}->{n_out}")
+        assert_bits_equal(Xd.grad[rows.to(dev)], K.pam_matmul_fwd(G[rows], W), f"dX {k_in}->{n_out}")
+        cols = torch.arange(0, k_in, 7)
+        assert_bits_equal(Wd.grad[:, cols.to(dev)], K.pam_matmul_fwd(G.T, X[:, cols]), f"dW {k_in}->{n_out}")
 
 
 def test_square_gemm_4096_with_specials_sampled(pam, K, dev):
@@ -384,6 +394,88 @@ def test_square_gemm_4096_with_specials_sampled(pam, K, dev):
     perm = torch.randperm(n, generator=g).to(dev)
     Cp = ck.pam_matmul_fwd(Ad[perm], Bd, True, True, 1.0)
     assert bool(bits_equal(Cp, C[perm]).all())
+
+
+# ---- fused layer normalisation ---------------------------------------------------------------------
+
+def _ln_case(pam, dev, rows, width, affine, approx, offset, seed):
+    import ln_emulation as E
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, width, generator=g) * 2 + 0.3
+    gy = torch.randn(rows, width, generator=g)
+    w = (torch.randn(width, generator=g).abs() + 0.5) if affine else None
+    b = torch.randn(width, generator=g) if affine else None
+    xd = x.to(dev).requires_grad_()
+    wd = w.to(dev).requires_grad_() if affine else None
+    bd = b.to(dev).requires_grad_() if affine else None
+    y = pam.layer_norm(xd, (width,), wd, bd, 1e-5, offset=offset, approx_bwd=approx)
+    y.backward(gy.to(dev))
+    vec = 4 if width % 4 == 0 else 1
+    chain = E.Chain(offset, E.kernel_rowsum(vec), E.kernel_colsum(rows))
+    want = chain.run(x, w, b, gy, 1e-5, approx)
+    got = (y, xd.grad, wd.grad if affine else None, bd.grad if affine else None)
+    return got, want
+
+
+@pytest.mark.parametrize("width", [1, 2, 5, 48, 192, 200, 512, 1000, 1024])
+@pytest.mark.parametrize("approx", [True, False])
+def test_fused_layer_norm_bit_exact_against_replayed_chain(pam, dev, width, approx):
+    """The kernel against the CPU replay of its own chain in its own summation order: every output
+    and gradient bit for bit.  (The same chain summed with torch.sum is checked against the
+    reference's fixtures in test_oracle_golden.py.)"""
+    for affine, offset in ((True, None), (False, 1.0552)):
+        got, want = _ln_case(pam, dev, 37, width, affine, approx, offset, width)
+        for name, a, b in zip(("y", "dx", "dw", "db"), got, want):
+            if b is not None:
+                assert_bits_equal(a.reshape(b.shape), b, f"ln {name} width={width} affine={affine}")
+
+
+@pytest.mark.parametrize("approx", [True, False])
+def test_fused_layer_norm_matches_unfused_route(pam, dev, approx):
+    """Fused kernel vs the one-kernel-per-primitive composition on the GPU (torch.sum reductions):
+    same values up to the association of the row sums."""
+    from pam_b200 import fused
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(4, 197, 192, generator=g).to(dev)
+    gy = torch.randn(4, 197, 192, generator=g).to(dev)
+    ln = pam.LayerNorm(192, eps=1e-6, approx_bwd=approx).to(dev)
+    outs = []
+    for flag in (True, False):
+        fused.enabled = flag
+        try:
+            xi = x.clone().requires_grad_()
+            ln.zero_grad()
+            y = ln(xi)
+            y.backward(gy)
+            outs.append((y.detach(), xi.grad, ln.weight.grad.clone(), ln.bias.grad.clone()))
+        finally:
+            fused.enabled = True
+    for name, a, b in zip(("y", "dx", "dw", "db"), *outs):
+        if approx or name in ("y", "db"):
+            assert_close_nan(a, b, 2e-4, 2e-4 * float(b.abs().max()), f"ln {name}")
+        else:
+            # exact slopes are step functions of the centred values: a last-bit difference in a row
+            # mean can move an element across a step, so compare the bulk of the distribution
+            close = torch.isclose(a, b, rtol=2e-3, atol=2e-3 * float(b.abs().max()))
+            assert float(close.float().mean()) > 0.98, f"ln {name}"
+
+
+def test_layer_norm_config2_rows(pam, dev):
+    """BASELINE config 2: pam_ln over the 192-wide rows of X[12608 x 192], gamma = 1, beta = 0,
+    approx_bwd: full size on the GPU against the replayed chain on a sample of rows."""
+    import ln_emulation as E
+    g = torch.Generator().manual_seed(12)
+    x, gy = torch.randn(12608, 192, generator=g), torch.randn(12608, 192, generator=g)
+    ln = pam.LayerNorm(192, eps=1e-6, approx_bwd=True).to(dev)
+    xd = x.to(dev).requires_grad_()
+    y = ln(xd)
+    y.backward(gy.to(dev))
+    rows = torch.randperm(12608, generator=g)[:64]
+    chain = E.Chain(None, E.kernel_rowsum(4), E.torch_colsum)
+    wy, wdx, _, _ = chain.run(x[rows], torch.ones(192), torch.zeros(192), gy[rows], 1e-6, True)
+    assert_bits_equal(y[rows.to(dev)], wy, "y")
+    assert_bits_equal(xd.grad[rows.to(dev)], wdx, "dx")
+    assert_close_nan(ln.bias.grad, gy.sum(0), 1e-4, 1e-3, "db")
 
 
 def test_abi_rejects_bad_arguments_on_gpu(pam, dev):

@@ -165,3 +165,21 @@ def test_pow_and_adam_against_reference(oracle, golden):
         assert_bits_equal(p, golden[f"adam/p{step}"], f"adam p step {step}")
         assert_bits_equal(m, golden[f"adam/m{step}"])
         assert_bits_equal(v, golden[f"adam/v{step}"])
+
+
+@pytest.mark.parametrize("oname,mode", CASES_EW)
+def test_fused_layer_norm_chain_equals_reference(oracle, golden, oname, mode):
+    """The primitive-by-primitive chain that the fused pam_ln kernel evaluates (tests/ln_emulation.py),
+    summed with torch.sum, is the reference's layer_norm forward and backward bit for bit."""
+    import ln_emulation as E
+    chain = E.Chain(None if oname == "none" else 1.0552, E.torch_rowsum, E.torch_colsum)
+    approx = mode == "approx"
+    k = f"{oname}/{mode}"
+    y, dx, dw, db = chain.run(golden["ln/x"], golden["ln/w"], golden["ln/b"], golden["ln/g"], 1e-5, approx)
+    assert_bits_equal(y.view(7, 3, 48), golden[f"ln/affine/{k}/y"])
+    assert_bits_equal(dx.view(7, 3, 48), golden[f"ln/affine/{k}/dx"])
+    assert_bits_equal(dw, golden[f"ln/affine/{k}/dw"])
+    assert_bits_equal(db, golden[f"ln/affine/{k}/db"])
+    y, dx, _, _ = chain.run(golden["ln/x"], None, None, golden["ln/g"], 1e-6, approx)
+    assert_bits_equal(y.view(7, 3, 48), golden[f"ln/plain/{k}/y"])
+    assert_bits_equal(dx.view(7, 3, 48), golden[f"ln/plain/{k}/dx"])
