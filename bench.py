@@ -39,6 +39,11 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of X in the CPU sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None,
+                    help="run one kernel in isolation (for profiling) instead of the benchmark: "
+                         "gemm | gemm_specials | deit_gemms | mul | layer_norm_fwd | layer_norm_bwd")
+    ap.add_argument("--size", type=int, default=4096, help="--case size: GEMM edge, or log2 of the element count")
+    ap.add_argument("--reps", type=int, default=2)
     return ap.parse_args()
 
 
@@ -266,6 +271,67 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ---- single kernels, for profilers -------------------------------------------------------------------
+
+def run_case(args):
+    """Launches one kernel `--reps` times after one warm-up and prints its CUDA-event time.  Meant
+    to be wrapped by ncu (`-k regex:<kernel> -s 1 -c 1`); sizes default to a few hundred MB."""
+    import pam_b200 as pam
+    from pam_b200 import cuda_bindings as cb
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(7)
+    n = args.size
+    if args.case in ("gemm", "gemm_specials"):
+        A, B = torch.randn(n, n, generator=g), torch.randn(n, n, generator=g)
+        if args.case == "gemm_specials":       # 1% zeros / denormals / +-1e30 / +-1e-30
+            vals = torch.tensor([0.0, -0.0, 1e-40, -1e-40, 1.4e-45, -1.4e-45, 1e30, -1e30, 1e-30, -1e-30])
+            for t in (A, B):
+                idx = torch.randperm(t.numel(), generator=g)[: t.numel() // 100]
+                t.view(-1)[idx] = vals[torch.arange(idx.numel()) % 10]
+        A, W = A.to(dev), B.to(dev)
+        fn, work, unit = (lambda: cb._matmul(0, A, W.T, 1.0, 2)), float(n) ** 3, "MAC"
+    elif args.case == "deit_gemms":
+        d = make_inputs(1234, device=dev)
+
+        def fn():
+            for X, W, G in zip(d["X"], d["W"], d["G"]):
+                cb._matmul(0, X, W.T, 1.0, 2)
+                cb._matmul(0, G, W, 1.0, 2)
+                cb._matmul(0, X.T, G, 1.0, 2)
+        work, unit = float(MACS_PER_STEP), "MAC"
+    elif args.case == "mul":
+        count = 1 << n if n < 40 else n
+        a, b = torch.randn(count, device=dev), torch.randn(count, device=dev)
+        fn, work, unit = (lambda: cb.cuda_kernels.pam_fwd(a, b, 1.0)), 12.0 * count, "B"
+    elif args.case in ("layer_norm_fwd", "layer_norm_bwd"):
+        rows = (1 << n if n < 40 else n) // LN_WIDTH
+        x = torch.randn(rows, LN_WIDTH, device=dev, requires_grad=True)
+        gy = torch.randn(rows, LN_WIDTH, device=dev)
+        ln = pam.LayerNorm(LN_WIDTH, eps=1e-6, approx_bwd=True).to(dev)
+        if args.case == "layer_norm_fwd":
+            def fn():
+                with torch.no_grad():
+                    ln(x)
+            work = 8.0 * rows * LN_WIDTH
+        else:
+            y = ln(x)
+            fn = lambda: torch.autograd.grad(y, (x, ln.weight, ln.bias), gy, retain_graph=True)
+            work = 12.0 * rows * LN_WIDTH
+        unit = "B"
+    else:
+        raise SystemExit(f"unknown --case {args.case}")
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.reps
+    print(json.dumps({"case": args.case, "size": n, "ms": ms, f"G{unit}_per_s": work / ms / 1e6}))
+
+
 # ---- CPU baseline / reference arm ---------------------------------------------------------------------
 
 def cpu_sample(args, target_seconds):
@@ -282,7 +348,7 @@ def cpu_sample(args, target_seconds):
         N.matmul(d["X"][0][:8], d["W"][0].T)
         probe = (time.perf_counter() - t0) / (8 * 192 * 576)          # seconds per MAC
         per_row = 3 * sum(k * n for k, n in LAYERS) * probe
-        rows = int(max(4, min(256, target_seconds / max(per_row, 1e-12))))
+        rows = int(max(4, min(TOKENS, target_seconds / max(per_row, 1e-12))))
     macs = 3 * rows * sum(k * n for k, n in LAYERS)
     t0 = time.perf_counter()
     for X, W, G in zip(d["X"], d["W"], d["G"]):
@@ -328,7 +394,9 @@ def run_reference(args):
 if __name__ == "__main__":
     a = parse()
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-    if a.impl == "reference":
+    if a.case:
+        run_case(a)
+    elif a.impl == "reference":
         run_reference(a)
     else:
         run_ours(a)

@@ -236,23 +236,44 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_kernel(const LnArgs a) {
     }
 }
 
-// dw[c] = sum over CTAs of partials[cta][0][c], db likewise, in CTA order.
-__global__ void ln_param_grad_kernel(const float* __restrict__ partials, float* __restrict__ dw,
-                                     float* __restrict__ db, int ctas, int width) {
-    const int col = blockIdx.x * blockDim.x + threadIdx.x;
-    if (col >= width) return;
+// dw[c] = sum over CTAs of partials[cta][0][c], db likewise.  One CTA per 32 columns; warp j adds
+// the partials of CTAs j, j + 8, j + 16, ... in that order, then the eight warp sums are added in
+// warp order.
+constexpr int kGradWarps = 8;
+__global__ void __launch_bounds__(kGradWarps * 32) ln_param_grad_kernel(const float* __restrict__ partials,
+                                                                       float* __restrict__ dw, float* __restrict__ db,
+                                                                       int ctas, int width) {
+    __shared__ float stage[2][kGradWarps][32];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int col = blockIdx.x * 32 + lane;
     float sw = 0.0f, sb = 0.0f;
-    for (int k = 0; k < ctas; ++k) {
-        sw = fadd(sw, partials[((int64_t)k * 2) * width + col]);
-        sb = fadd(sb, partials[((int64_t)k * 2 + 1) * width + col]);
+    if (col < width) {
+        for (int k = wid; k < ctas; k += kGradWarps) {
+            sw = fadd(sw, __ldg(partials + ((int64_t)k * 2) * width + col));
+            sb = fadd(sb, __ldg(partials + ((int64_t)k * 2 + 1) * width + col));
+        }
     }
-    if (dw) dw[col] = sw;
-    if (db) db[col] = sb;
+    stage[0][wid][lane] = sw;
+    stage[1][wid][lane] = sb;
+    __syncthreads();
+    if (wid == 0 && col < width) {
+        sw = stage[0][0][lane];
+        sb = stage[1][0][lane];
+#pragma unroll
+        for (int k = 1; k < kGradWarps; ++k) {
+            sw = fadd(sw, stage[0][k][lane]);
+            sb = fadd(sb, stage[1][k][lane]);
+        }
+        if (dw) dw[col] = sw;
+        if (db) db[col] = sb;
+    }
 }
 
-int pick_grid(int64_t rows) {
+// Forward: enough CTAs for 64 resident warps per SM.  Backward: fewer, longer-lived CTAs (each warp
+// walks several rows), which keeps the per-CTA partial sums for dweight / dbias few.
+int pick_grid(int64_t rows, bool backward) {
     const int64_t want = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
-    const int64_t cap = (int64_t)sm_count() * 16;            // 16 CTAs x 4 warps: 64 warps per SM
+    const int64_t cap = (int64_t)sm_count() * (backward ? 4 : 16);
     return (int)(want < cap ? want : cap);
 }
 
@@ -294,12 +315,12 @@ int pamk_layer_norm_fwd(const float* x, const float* weight, const float* bias, 
     if (rows == 0) return PAMK_OK;
     if (!x || !y) return PAMK_ERR_ARG;
     LnArgs a{x, weight, bias, nullptr, y, nullptr, rows, (int)width, (float)width, eps, offset_bits(offset)};
-    return launch<false, false>(a, pick_grid(rows), static_cast<cudaStream_t>(stream));
+    return launch<false, false>(a, pick_grid(rows, false), static_cast<cudaStream_t>(stream));
 }
 
 size_t pamk_layer_norm_bwd_workspace_bytes(int64_t rows, int64_t width) {
     if (rows <= 0 || width <= 0) return 0;
-    return (size_t)pick_grid(rows) * 2 * (size_t)width * sizeof(float);
+    return (size_t)pick_grid(rows, true) * 2 * (size_t)width * sizeof(float);
 }
 
 int pamk_layer_norm_bwd(const float* x, const float* weight, const float* dy, float* dx,
@@ -315,7 +336,7 @@ int pamk_layer_norm_bwd(const float* x, const float* weight, const float* dy, fl
         return PAMK_OK;
     }
     if (!x || !dy || !dx) return PAMK_ERR_ARG;
-    const int grid = pick_grid(rows);
+    const int grid = pick_grid(rows, true);
     const bool params = dweight || dbias;
     if (params && (!workspace || workspace_bytes < pamk_layer_norm_bwd_workspace_bytes(rows, width) ||
                    (reinterpret_cast<uintptr_t>(workspace) & 15u)))
@@ -324,8 +345,8 @@ int pamk_layer_norm_bwd(const float* x, const float* weight, const float* dy, fl
              rows, (int)width, (float)width, eps, offset_bits(offset)};
     const int rc = approx_bwd ? launch<true, true>(a, grid, st) : launch<true, false>(a, grid, st);
     if (rc != PAMK_OK || !params) return rc;
-    ln_param_grad_kernel<<<(unsigned)((width + 127) / 128), 128, 0, st>>>(static_cast<const float*>(workspace), dweight,
-                                                                         dbias, grid, (int)width);
+    ln_param_grad_kernel<<<(unsigned)((width + 31) / 32), kGradWarps * 32, 0, st>>>(
+        static_cast<const float*>(workspace), dweight, dbias, grid, (int)width);
     return check_launch();
 }
 

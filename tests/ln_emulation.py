@@ -105,20 +105,26 @@ def kernel_rowsum(vec):
     return rowsum
 
 
-def kernel_colsum(rows_total, warps_per_cta=4):
-    """Order of the dweight / dbias sums when every warp owns at most one row (rows <= 4 x grid
-    cap): the four warps of a CTA are added in order, then the CTAs in order, from +0."""
+def kernel_colsum(rows_total, grid, warps_per_cta=4, grad_warps=8):
+    """Order of the dweight / dbias sums in the kernel: warp w of CTA c adds its rows
+    (c*4 + w, + grid*4, ...) in order from +0; the four warps of a CTA are added in order; the
+    second kernel's warp j adds the CTA sums j, j + 8, ... in order from +0 and the eight warp
+    sums are added in order."""
     def colsum(t):
         rows, n = t.shape
-        ctas = -(-rows // warps_per_cta)
-        padded = torch.zeros(ctas * warps_per_cta, n)
-        padded[:rows] = t
-        padded = padded.view(ctas, warps_per_cta, n)
-        total = torch.zeros(n)
-        for cta in range(ctas):
-            part = padded[cta, 0]
-            for wdx in range(1, warps_per_cta):
-                part = part + padded[cta, wdx]
-            total = total + part
+        nwarps = grid * warps_per_cta
+        warp_sums = torch.zeros(nwarps, n)
+        for r in range(rows):
+            warp_sums[r % nwarps] = warp_sums[r % nwarps] + t[r]
+        ws = warp_sums.view(grid, warps_per_cta, n)
+        cta = ws[:, 0]
+        for wdx in range(1, warps_per_cta):
+            cta = cta + ws[:, wdx]
+        subs = torch.zeros(grad_warps, n)
+        for k in range(grid):
+            subs[k % grad_warps] = subs[k % grad_warps] + cta[k]
+        total = subs[0]
+        for j in range(1, grad_warps):
+            total = total + subs[j]
         return total
     return colsum
