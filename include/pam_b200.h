@@ -115,6 +115,31 @@ int pamk_matmul_auto_split(int64_t batch, int64_t M, int64_t N, int64_t K);
  * Results do not depend on the tile. */
 int pamk_matmul_set_tile_policy(int policy);
 
+/* Split-K PAM product for callers that cannot allocate.  It has no counterpart in the reference.
+ *
+ * pamk_matmul with split_k > 1 needs a scratch buffer for the partial sums, which the caller has
+ * to allocate.  Some callers cannot: code running inside a CUDA stream capture or a real-time loop
+ * where cudaMalloc is forbidden, a plugin whose host gives it fixed input / output buffers and no
+ * allocator, or a process that has handed all device memory to another pool.  This variant takes
+ * the same operands and computes the same result (bit for bit the same as pamk_matmul with the
+ * same split_k), but keeps the partial sums in a fixed 32 MiB array inside the library, so it
+ * never calls cudaMalloc, cudaFree or any allocating routine.
+ *
+ *   - limit: split_k * batch * M * N floats must fit in pamk_matmul_static_scratch_bytes();
+ *     larger problems are refused with PAMK_ERR_SIZE (nothing is launched); split_k must be >= 1;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress);
+ *     make that first call outside any stream capture;
+ *   - every call on a device shares the one array.  Nothing in it has to start at zero: each call
+ *     overwrites every partial sum it later reads, so stale contents from an earlier call are never
+ *     seen.  Two calls that overlap on the GPU (different streams, or two host threads) would race
+ *     on the array: serialise them. */
+size_t pamk_matmul_static_scratch_bytes(void);
+int pamk_matmul_static_scratch(const float* A, const float* B, float* C,
+                               int64_t batch, int64_t M, int64_t N, int64_t K,
+                               int64_t sAb, int64_t sAm, int64_t sAk,
+                               int64_t sBb, int64_t sBk, int64_t sBn,
+                               float offset, int split_k, void* stream);
+
 /* Exact-gradient product: out[z][i][j] = sum_k pam_bwd(D[z][i][j], other, delta) with
  * (other, delta) = (R[k][j], L[i][k]) if delta_l else (L[i][k], R[k][j]).
  * Replaces pam_matmul_bwd / pam_bmm_bwd: pam_matmul_bwd_caller, cuda_kernels.cu:834-927. */

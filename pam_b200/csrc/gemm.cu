@@ -499,6 +499,32 @@ bool dims_ok(int64_t batch, int64_t M, int64_t N, int64_t K) {
     return batch >= 0 && M >= 0 && N >= 0 && K >= 0 && batch <= lim && M <= lim && N <= lim && K <= lim;
 }
 
+// ---- allocation-free split-K --------------------------------------------------------------------
+// Scratch for pamk_matmul_static_scratch: lives in the library image, so every GPU that loads the
+// library holds these 32 MiB from load until exit, and no allocation is ever needed for it.
+constexpr size_t kStaticScratchFloats = size_t(8) << 20;
+static __device__ __align__(256) float g_splitk_scratch[kStaticScratchFloats];
+
+// In host code `g_splitk_scratch` is only a handle for the symbol; the device address has to be
+// asked for, per device, with that device current.
+constexpr int kMaxDevices = 64;
+float* g_scratch_addr[kMaxDevices] = {};
+
+int static_scratch(float** out) {
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return record_cuda_error(err);
+    if (dev < 0 || dev >= kMaxDevices) return PAMK_ERR_SIZE;
+    if (g_scratch_addr[dev] == nullptr) {
+        void* ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, g_splitk_scratch);
+        if (err != cudaSuccess) return record_cuda_error(err);
+        g_scratch_addr[dev] = static_cast<float*>(ptr);
+    }
+    *out = g_scratch_addr[dev];
+    return PAMK_OK;
+}
+
 }  // namespace
 }  // namespace pamk
 
@@ -547,6 +573,40 @@ int pamk_matmul(int mul_kind, const float* A, const float* B, float* C,
     p.off = offset_bits(offset);
     p.bias_sub = isub(kBias, p.off);
     return run(mul_kind == PAMK_MUL_PAM ? kPam : kStd, p, a_kc, b_kc, split_k, workspace, workspace_bytes,
+               static_cast<cudaStream_t>(stream));
+}
+
+size_t pamk_matmul_static_scratch_bytes(void) { return kStaticScratchFloats * sizeof(float); }
+
+int pamk_matmul_static_scratch(const float* A, const float* B, float* C,
+                               int64_t batch, int64_t M, int64_t N, int64_t K,
+                               int64_t sAb, int64_t sAm, int64_t sAk,
+                               int64_t sBb, int64_t sBk, int64_t sBn,
+                               float offset, int split_k, void* stream) {
+    if (!dims_ok(batch, M, N, K)) return batch < 0 || M < 0 || N < 0 || K < 0 ? PAMK_ERR_ARG : PAMK_ERR_SIZE;
+    if (split_k < 1) return PAMK_ERR_ARG;
+    if (batch == 0 || M == 0 || N == 0) return PAMK_OK;
+    if (C == nullptr) return PAMK_ERR_ARG;
+    // every partial sum must fit in the fixed array
+    if ((double)split_k * (double)batch * (double)M * (double)N > (double)kStaticScratchFloats) return PAMK_ERR_SIZE;
+    GemmParams p{};
+    bool a_kc = true, b_kc = true;
+    if (K > 0) {
+        int rc = operand_layout(A, sAm, sAk, (int)M, (int)K, &a_kc);
+        if (rc != PAMK_OK) return rc;
+        rc = operand_layout(B, sBn, sBk, (int)N, (int)K, &b_kc);
+        if (rc != PAMK_OK) return rc;
+    }
+    float* scratch = nullptr;
+    const int rc = static_scratch(&scratch);
+    if (rc != PAMK_OK) return rc;
+    p.A = {A, sAb, sAm, sAk};
+    p.B = {B, sBb, sBn, sBk};
+    p.C = C;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
+    p.off = offset_bits(offset);
+    p.bias_sub = isub(kBias, p.off);
+    return run(kPam, p, a_kc, b_kc, split_k, scratch, kStaticScratchFloats * sizeof(float),
                static_cast<cudaStream_t>(stream));
 }
 
