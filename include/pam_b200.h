@@ -170,6 +170,21 @@ int pamk_layer_norm_bwd(const float* x, const float* weight, const float* dy, fl
                         float* dweight, float* dbias, int64_t rows, int64_t width, float eps, float offset,
                         int approx_bwd, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- fused PAM Adam ------------------------------------------------------------------------------
+ * Replaces the per-tensor launch chain of the reference's PAM Adam
+ * (submodules/fairseq/fairseq/optim/adam.py:226-252 over pam.mul / pam.div / pam.pow):
+ *   m = pam(m, beta1) + pam(g, 1-beta1);  v = pam(v, beta2) + pam(pam(g, g), 1-beta2);
+ *   p -= pam(p, decay) [if decay != 0];   p -= pam(pad(m, pow(v, 0.5) + eps), step_size)
+ * in place, for `count` tensors in one call.  p, g, m, v, n are HOST arrays of `count` entries:
+ * device pointers to the fp32 parameter, gradient, exp_avg, exp_avg_sq, and their element counts.
+ * The scalars are the reference's Python doubles rounded to fp32 once (as pam/utils.py:13 does):
+ * decay = weight_decay * lr, step_size = lr * sqrt(1 - beta2^t) / (1 - beta1^t).
+ * Results are bit-identical to the reference's chain (purely per-element arithmetic). */
+int pamk_adam_step(float* const* p, const float* const* g, float* const* m, float* const* v,
+                   const int64_t* n, int count,
+                   float beta1, float one_minus_beta1, float beta2, float one_minus_beta2,
+                   float eps, float decay, float step_size, float offset, void* stream);
+
 /* ---- roofline measurement --------------------------------------------------------------------
  * No counterpart in the reference.  Runs register-only chains of the instructions a PAM
  * multiply-accumulate is made of and reports how many chain steps ran in how many milliseconds;

@@ -105,4 +105,22 @@ def softmax_supported(x, dim):
 # ---- Adam --------------------------------------------------------------------------------------------
 
 def adam_supported(p, grad):
-    return False
+    return (enabled and p.is_cuda and p.dtype == torch.float32 and grad.dtype == torch.float32 and
+            p.is_contiguous() and grad.is_contiguous() and grad.device == p.device)
+
+
+def adam_step(tensors, *, beta1, beta2, eps, step_size, decay, offset=None):
+    """One PAM Adam update, in place, of every (param, grad, exp_avg, exp_avg_sq) in `tensors`
+    (all fp32, contiguous, on one CUDA device) with shared scalars.  The scalars arrive as Python
+    doubles and are rounded to fp32 here, once, like the reference's scalar-to-tensor promotion."""
+    import ctypes
+    if not tensors:
+        return
+    dev = tensors[0][0].device
+    count = len(tensors)
+    ptrs = [(ctypes.c_void_p * count)(*[t[k].data_ptr() for t in tensors]) for k in range(4)]
+    sizes = (ctypes.c_int64 * count)(*[t[0].numel() for t in tensors])
+    with _lib.device_guard(dev):
+        status = _lib.lib().pamk_adam_step(*ptrs, sizes, count, beta1, 1 - beta1, beta2, 1 - beta2, eps,
+                                           decay, step_size, _offset(offset), _lib.stream_ptr(dev))
+    _lib.check(status, "pamk_adam_step")

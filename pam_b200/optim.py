@@ -37,6 +37,14 @@ class Adam(torch.optim.Optimizer):
     def supports_flat_params(self):
         return True
 
+    @staticmethod
+    def _scalars(group, step):
+        """step_size and decay, formed in double on the host (adam.py:240-243) and rounded to fp32
+        only when they meet a tensor (pam/utils.py:13)."""
+        beta1, beta2 = group["betas"]
+        step_size = group["lr"] * math.sqrt(1 - beta2 ** step) / (1 - beta1 ** step)
+        return step_size, group["weight_decay"] * group["lr"]
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = None
@@ -46,6 +54,7 @@ class Adam(torch.optim.Optimizer):
         ops = self.op_dict
         for group in self.param_groups:
             beta1, beta2 = group["betas"]
+            batches = {}             # step count -> tensors that share every scalar of the rule
             for p in group["params"]:
                 if p.grad is None:
                     continue
@@ -66,25 +75,27 @@ class Adam(torch.optim.Optimizer):
                     state["exp_avg"] = state["exp_avg"].to(p32)
                     state["exp_avg_sq"] = state["exp_avg_sq"].to(p32)
                 state["step"] += 1
-                # scalars are formed in double on the host and rounded to fp32 once, when they
-                # meet a tensor (adam.py:240-243, pam/utils.py:13)
-                bias1 = 1 - beta1 ** state["step"]
-                bias2 = 1 - beta2 ** state["step"]
-                step_size = group["lr"] * math.sqrt(bias2) / bias1
-                decay = group["weight_decay"] * group["lr"]
 
-                if self._fusable and fused.adam_supported(p32, grad):
-                    fused.adam_step(p32, grad, state["exp_avg"], state["exp_avg_sq"], beta1=beta1, beta2=beta2,
-                                    eps=group["eps"], step_size=step_size, decay=decay)
-                else:
-                    m, v = state["exp_avg"], state["exp_avg_sq"]
-                    m.copy_(ops["mul"](m, beta1) + ops["mul"](grad, 1 - beta1))
-                    v.copy_(ops["mul"](v, beta2))
-                    v += ops["mul"](ops["mul"](grad, grad), 1 - beta2)
-                    denom = ops["pow"](v, 0.5) + group["eps"]
-                    if group["weight_decay"] != 0:
-                        p32 -= ops["mul"](p32, decay)
-                    p32 -= ops["mul"](ops["div"](m, denom), step_size)
+                if self._fusable and not half and fused.adam_supported(p32, grad):
+                    batches.setdefault(state["step"], []).append((p32, grad, state["exp_avg"], state["exp_avg_sq"]))
+                    continue
+                step_size, decay = self._scalars(group, state["step"])
+                m, v = state["exp_avg"], state["exp_avg_sq"]
+                m.copy_(ops["mul"](m, beta1) + ops["mul"](grad, 1 - beta1))
+                v.copy_(ops["mul"](v, beta2))
+                v += ops["mul"](ops["mul"](grad, grad), 1 - beta2)
+                denom = ops["pow"](v, 0.5) + group["eps"]
+                if group["weight_decay"] != 0:
+                    p32 -= ops["mul"](p32, decay)
+                p32 -= ops["mul"](ops["div"](m, denom), step_size)
                 if half:
                     p.copy_(p32)
+            for step, tensors in batches.items():
+                step_size, decay = self._scalars(group, step)
+                by_device = {}
+                for t in tensors:
+                    by_device.setdefault(t[0].device, []).append(t)
+                for same_device in by_device.values():
+                    fused.adam_step(same_device, beta1=beta1, beta2=beta2, eps=group["eps"],
+                                    step_size=step_size, decay=decay if group["weight_decay"] != 0 else 0.0)
         return loss

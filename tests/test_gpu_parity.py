@@ -482,6 +482,40 @@ def test_layer_norm_config2_rows(pam, dev):
     assert_close_nan(ln.bias.grad, gy.sum(0), 1e-4, 1e-3, "db")
 
 
+# ---- fused Adam ---------------------------------------------------------------------------------------
+
+def test_fused_adam_many_tensors_bit_exact(pam, oracle, dev):
+    """A table of tensors of awkward sizes (empty, one element, not a multiple of four, views that
+    start off a 16-byte boundary, more tensors than one launch holds) through three steps, against
+    the oracle's restatement of the reference rule; and the unfused op-dictionary route likewise."""
+    from pam_b200 import optim
+    g = torch.Generator().manual_seed(77)
+    sizes = [0, 1, 3, 4, 5, 257, 1024, 4099] + [33 + 7 * i for i in range(30)]
+    for cfg in ("pam", '{"type": "pam"}'):
+        backing = [torch.randn(n + 1, generator=g) for n in sizes]
+        params = [torch.nn.Parameter(b.to(dev)[1:] if i % 3 == 0 else b.to(dev)[:-1].clone()) for i, b in enumerate(backing)]
+        host = [p.detach().cpu().clone() for p in params]
+        ms = [torch.zeros_like(h) for h in host]
+        vs = [torch.zeros_like(h) for h in host]
+        opt = optim.Adam(params, lr=5e-4, betas=(0.9, 0.98), eps=1e-8, weight_decay=1e-4, opt_functional_cfg=cfg)
+        for step in (1, 2, 3):
+            grads = [torch.randn(h.shape, generator=g) * 0.1 for h in host]
+            if step == 2:
+                for gr in grads:
+                    gr[::5] = 0.0
+            for p, gr in zip(params, grads):
+                p.grad = gr.to(dev)
+            opt.step()
+            for i in range(len(host)):
+                host[i], ms[i], vs[i] = oracle.adam_step(host[i], grads[i], ms[i], vs[i], step=step, lr=5e-4,
+                                                         betas=(0.9, 0.98), eps=1e-8, weight_decay=1e-4)
+        for i, p in enumerate(params):
+            assert_bits_equal(p.detach(), host[i], f"{cfg} p[{i}]")
+            if sizes[i]:
+                assert_bits_equal(opt.state[p]["exp_avg"], ms[i], f"{cfg} m[{i}]")
+                assert_bits_equal(opt.state[p]["exp_avg_sq"], vs[i], f"{cfg} v[{i}]")
+
+
 def test_abi_rejects_bad_arguments_on_gpu(pam, dev):
     from pam_b200 import _lib
     h = _lib.lib()
