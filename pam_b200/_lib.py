@@ -9,8 +9,11 @@ import pathlib
 
 import torch
 
+import os
+
 _PKG = pathlib.Path(__file__).resolve().parent
-LIB_PATH = _PKG / "libpam_b200.so"
+# PAM_B200_LIBRARY points at another build of the same library (A/B comparisons of kernel variants).
+LIB_PATH = pathlib.Path(os.environ.get("PAM_B200_LIBRARY") or _PKG / "libpam_b200.so")
 
 FULL, SCALAR, ROW, COL, IMM = 0, 1, 2, 3, 4
 MUL_PAM, MUL_STANDARD = 0, 1

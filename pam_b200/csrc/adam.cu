@@ -104,11 +104,11 @@ int pamk_adam_step(float* const* p, const float* const* g, float* const* m, floa
     if (!p || !g || !m || !v || !n) return PAMK_ERR_ARG;
     const AdamScalars s{beta1, one_minus_beta1, beta2, one_minus_beta2, eps, decay, step_size, offset_bits(offset)};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    for (int first = 0; first < count; first += kTensorsPerLaunch) {
+    for (int k = 0; k < count;) {
         AdamTable t{};
         int used = 0;
         int64_t longest = 0;
-        for (int k = first; k < count && used < kTensorsPerLaunch; ++k) {
+        for (; k < count && used < kTensorsPerLaunch; ++k) {     // k carries on where the last table ended
             if (n[k] < 0) return PAMK_ERR_ARG;
             if (n[k] == 0) continue;
             if (!p[k] || !g[k] || !m[k] || !v[k]) return PAMK_ERR_ARG;

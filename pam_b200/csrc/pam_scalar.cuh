@@ -50,6 +50,7 @@ PAM_HD float quiet_nan() { return i2f(0x7fc00000); }
 // wrap-around integer add on bit patterns
 PAM_HD int32_t iadd(int32_t a, int32_t b) { return (int32_t)((uint32_t)a + (uint32_t)b); }
 PAM_HD int32_t isub(int32_t a, int32_t b) { return (int32_t)((uint32_t)a - (uint32_t)b); }
+PAM_HD int32_t iadd3(int32_t a, int32_t b, int32_t c) { return (int32_t)((uint32_t)a + (uint32_t)b + (uint32_t)c); }
 
 // float offset -> integer added to the result's bit pattern (cuda_kernels.cu:168)
 PAM_HD int32_t offset_bits(float offset) { return isub(f2i(offset), kBias); }
