@@ -143,9 +143,10 @@ __global__ void __launch_bounds__(kThreads, NIN > 2 ? 6 : 8) ew_kernel(Op op, Op
     }
 }
 
-bool operand_ok(const Operand& o) {
+// An empty launch (n == 0) may carry null pointers: an empty tensor has no storage.
+bool operand_ok(const Operand& o, int64_t n) {
     if (o.kind < PAMK_FULL || o.kind > PAMK_IMM) return false;
-    return o.kind == PAMK_IMM || o.p != nullptr;
+    return o.kind == PAMK_IMM || o.p != nullptr || n == 0;
 }
 
 bool operand_vectorisable(const Operand& o, int64_t inner) {
@@ -160,7 +161,7 @@ bool operand_vectorisable(const Operand& o, int64_t inner) {
 template <class Op, int NIN>
 int launch(Op op, Operand o0, Operand o1, Operand o2, float* out, int64_t n, int64_t inner, void* stream) {
     if (n < 0 || (out == nullptr && n > 0)) return PAMK_ERR_ARG;
-    if (!operand_ok(o0) || (NIN > 1 && !operand_ok(o1)) || (NIN > 2 && !operand_ok(o2))) return PAMK_ERR_ARG;
+    if (!operand_ok(o0, n) || (NIN > 1 && !operand_ok(o1, n)) || (NIN > 2 && !operand_ok(o2, n))) return PAMK_ERR_ARG;
     const bool needs_inner = o0.kind == PAMK_ROW || o0.kind == PAMK_COL ||
                              (NIN > 1 && (o1.kind == PAMK_ROW || o1.kind == PAMK_COL)) ||
                              (NIN > 2 && (o2.kind == PAMK_ROW || o2.kind == PAMK_COL));

@@ -12,7 +12,8 @@
 //     operand fetch is four 128-bit shared-memory loads per 64 products;
 //   * operands are staged global -> registers -> shared one K-slab (16) ahead of the arithmetic
 //     (double-buffered shared memory, one barrier per slab); while they pass through registers
-//     both sides are laid out [k][row] whatever their layout in global memory (the four
+//     the A side is pre-biased (bits - (0x3f800000 - offset)) so that the product is a single
+//     add, both sides are laid out [k][row] whatever their layout in global memory (the four
 //     row-/column-major combinations of the reference become two loader variants per side), and
 //     the exponent range of the slab is recorded;
 //   * the reference's per-product range rule (flush below 1e-37, NaN above 1e37 or for
@@ -22,13 +23,16 @@
 //     exactly.  Either way every product equals the reference's bit for bit;
 //   * each output is summed by one thread, strictly in k order, from +0.0f — the same order as
 //     the reference's kernel (cuda_kernels.cu:608-629), so without split-K the sums are
-//     bit-identical too.  With split-K each K range is such a sum; the CTA that finishes a tile
-//     last adds the ranges' partial sums in range order, in the same launch.
+//     bit-identical too.
 //
 // The same skeleton serves true-multiply products (standard_matmul) and the exact-gradient
 // product (pam_matmul_bwd_kernel, cuda_kernels.cu:729-832).
 #include "common.cuh"
 #include "pam_scalar.cuh"
+
+#ifndef PAMK_IADD3
+#define PAMK_IADD3 0
+#endif
 
 namespace pamk {
 namespace {
@@ -46,9 +50,7 @@ struct GemmParams {
     MatArg A, B;
     const float* D;           // exact-gradient product only: the operand the slope depends on
     int64_t sDb, sDm, sDn;
-    float* C;                 // [batch][M][N]
-    float* part;              // split-K scratch: [split][batch][M][N] partial sums
-    int* counters;            // split-K scratch: one arrival counter per output tile, zero on entry
+    float* C;                 // [batch][M][N], or [split][batch][M][N] partials when splits > 1
     int M, N, K, batch;
     int splits, k_chunk;      // K is cut into `splits` ranges of k_chunk (a multiple of the slab)
     int32_t bias_sub;         // 0x3f800000 - offset_bits
@@ -168,59 +170,6 @@ __device__ __forceinline__ int classify(int minA, int maxA, int minB, int maxB) 
     return bounded ? (large ? kFast : kFlush) : kFull;
 }
 
-// ---- split-K: in-launch reduction -------------------------------------------------------------------
-// Every K range writes its partial tile to scratch and then takes a ticket at the tile's counter.
-// The CTA that draws the last ticket adds the partial tiles in range order — so the result does not
-// depend on which CTA that is — and writes C.  Nobody waits for anybody.  Both helpers are kept out
-// of line so that they do not add to the register pressure of the main loop.
-__device__ __noinline__ bool arrived_last(const GemmParams& p, int z) {
-    __shared__ int is_last;
-    __threadfence();                       // this CTA's partial tile is visible before its ticket
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int* counter = p.counters + ((int64_t)z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-        const int ticket = atomicAdd(counter, 1);
-        is_last = ticket == p.splits - 1;
-        if (is_last) *counter = 0;         // every range has arrived: leave the counter ready for reuse
-    }
-    __syncthreads();
-    const bool last = is_last != 0;
-    if (last) __threadfence();
-    return last;
-}
-
-template <class T>
-__device__ __noinline__ void reduce_tile(const GemmParams& p, int z, int m0, int n0, bool vec_out) {
-    const int tx = threadIdx.x % T::TX, ty = threadIdx.x / T::TX;
-    const int64_t MN = (int64_t)p.M * p.N, stride = (int64_t)p.batch * MN;
-    const float* first = p.part + (int64_t)z * MN;
-    float* out = p.C + (int64_t)z * MN;
-    for (int i = 0; i < 8; ++i) {
-        const int row = m0 + ty * 4 + (i & 3) + (i >> 2) * (T::BM / 2);
-        if (row >= p.M) continue;
-        for (int h = 0; h < 2; ++h) {
-            const int col = n0 + tx * 4 + h * (T::BN / 2);
-            const int64_t at = (int64_t)row * p.N + col;
-            if (vec_out) {
-                if (col < p.N) {
-                    float4 v = __ldcg(reinterpret_cast<const float4*>(first + at));
-                    for (int r = 1; r < p.splits; ++r) {
-                        const float4 w = __ldcg(reinterpret_cast<const float4*>(first + at + r * stride));
-                        v.x = fadd(v.x, w.x); v.y = fadd(v.y, w.y); v.z = fadd(v.z, w.z); v.w = fadd(v.w, w.w);
-                    }
-                    *reinterpret_cast<float4*>(out + at) = v;
-                }
-            } else {
-                for (int j = 0; j < 4 && col + j < p.N; ++j) {
-                    float v = __ldcg(first + at + j);
-                    for (int r = 1; r < p.splits; ++r) v = fadd(v, __ldcg(first + at + j + r * stride));
-                    out[at + j] = v;
-                }
-            }
-        }
-    }
-}
-
 template <int MODE, class T, bool A_KC, bool B_KC, bool VEC>
 __global__ void __launch_bounds__(T::kThreads, MODE == kPam || MODE == kStd ? T::kCtasPerSm : T::kCtasPerSm / 2)
 gemm_kernel(const GemmParams p) {
@@ -266,8 +215,18 @@ gemm_kernel(const GemmParams p) {
 
     if (MODE == kPam && tid < 12) stats[tid >> 2][tid & 3] = (tid & 1) ? 0 : 0x7fffffff;   // [min, max, min, max]
 
-    // a PAM product is one three-input integer add: bits(a) + bits(b) + (offset - 0x3f800000)
+    // Two equivalent forms of the product's integer add.  Default: the A slab is pre-biased while it
+    // is staged, so a product is a two-input add.  PAMK_IADD3: operands stay raw and the bias is the
+    // third input of the add (measured slower on B200: the extra register read costs more than the
+    // staging pass saves).
+#if PAMK_IADD3
     const int32_t nbias = isub(0, p.bias_sub);
+#define PAMK_PRODUCT(x, y) iadd3((x), (y), nbias)
+#define PAMK_RAW(x) i2f(x)
+#else
+#define PAMK_PRODUCT(x, y) iadd((x), (y))
+#define PAMK_RAW(x) i2f(iadd((x), p.bias_sub))
+#endif
     float ra[T::kTasksA * 4], rb[T::kTasksB * 4];
     auto stage_load = [&](int k0) {
         load_slab<T, BM, T::kTasksA, A_KC, VEC>(ra, p.A, Ab, m0, p.M, k0, k_end, tid);
@@ -288,6 +247,10 @@ gemm_kernel(const GemmParams p) {
                 atomicMin(&stats[slot][2], lo_b);
                 atomicMax(&stats[slot][3], hi_b);
             }
+#if !PAMK_IADD3
+#pragma unroll
+            for (int c = 0; c < T::kTasksA * 4; ++c) ra[c] = i2f(isub(f2i(ra[c]), p.bias_sub));
+#endif
         }
         store_slab<T, BM, T::kTasksA, A_KC>(As[buf], ra, tid);
         store_slab<T, BN, T::kTasksB, B_KC>(Bs[buf], rb, tid);
@@ -327,18 +290,21 @@ gemm_kernel(const GemmParams p) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[i][j] = fadd(acc[i][j], i2f(iadd3(a[i], b[j], nbias)));
+                    for (int j = 0; j < 8; ++j) acc[i][j] = fadd(acc[i][j], i2f(PAMK_PRODUCT(a[i], b[j])));
             }
         } else if (MODE == kPam && path == kFlush) {
 #pragma unroll 2
             for (int kk = 0; kk < BK; ++kk) {
                 PAMK_FRAGMENTS(kk)
+                float araw[8];          // a[] holds pre-biased patterns; the product needs the values
+#pragma unroll
+                for (int i = 0; i < 8; ++i) araw[i] = PAMK_RAW(a[i]);
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const float mag = fabsf(fmul(i2f(a[i]), i2f(b[j])));
-                        if (mag > i2f(kFlushBits)) acc[i][j] = fadd(acc[i][j], i2f(iadd3(a[i], b[j], nbias)));
+                        const float mag = fabsf(fmul(araw[i], i2f(b[j])));
+                        if (mag > i2f(kFlushBits)) acc[i][j] = fadd(acc[i][j], i2f(PAMK_PRODUCT(a[i], b[j])));
                     }
             }
         } else {
@@ -346,12 +312,15 @@ gemm_kernel(const GemmParams p) {
             for (int kk = 0; kk < BK; ++kk) {
                 PAMK_FRAGMENTS(kk)
                 if constexpr (MODE == kPam) {
+                    float araw[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) araw[i] = PAMK_RAW(a[i]);
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            const float mag = fabsf(fmul(i2f(a[i]), i2f(b[j])));
-                            const float prod = mag <= i2f(kPassBits) ? i2f(iadd3(a[i], b[j], nbias)) : quiet_nan();
+                            const float mag = fabsf(fmul(araw[i], i2f(b[j])));
+                            const float prod = mag <= i2f(kPassBits) ? i2f(PAMK_PRODUCT(a[i], b[j])) : quiet_nan();
                             if (!(mag <= i2f(kFlushBits))) acc[i][j] = fadd(acc[i][j], prod);
                         }
                 } else if constexpr (MODE == kStd) {
@@ -379,31 +348,38 @@ gemm_kernel(const GemmParams p) {
     }
 
     // ---- epilogue ----------------------------------------------------------------------------
-    const int64_t MN = (int64_t)p.M * p.N;
-    const bool vec_out = (p.N & 3) == 0 && aligned16(p.C) && aligned16(p.part);
-    auto write_tile = [&](float* base) {
+    float* Cz = p.C + ((int64_t)sp * p.batch + z) * ((int64_t)p.M * p.N);
+    const bool vec_out = (p.N & 3) == 0 && aligned16(p.C);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int row = m0 + ty * 4 + (i & 3) + (i >> 2) * (BM / 2);
-            if (row >= p.M) continue;
-            float* crow = base + (int64_t)row * p.N;
+    for (int i = 0; i < 8; ++i) {
+        const int row = m0 + ty * 4 + (i & 3) + (i >> 2) * (BM / 2);
+        if (row >= p.M) continue;
+        float* crow = Cz + (int64_t)row * p.N;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int col = n0 + tx * 4 + h * (BN / 2);
-                if (vec_out) {
-                    if (col < p.N)
-                        *reinterpret_cast<float4*>(crow + col) =
-                            make_float4(acc[i][h * 4], acc[i][h * 4 + 1], acc[i][h * 4 + 2], acc[i][h * 4 + 3]);
-                } else {
+        for (int h = 0; h < 2; ++h) {
+            const int col = n0 + tx * 4 + h * (BN / 2);
+            if (vec_out) {
+                if (col < p.N)
+                    *reinterpret_cast<float4*>(crow + col) =
+                        make_float4(acc[i][h * 4], acc[i][h * 4 + 1], acc[i][h * 4 + 2], acc[i][h * 4 + 3]);
+            } else {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (col + j < p.N) crow[col + j] = acc[i][h * 4 + j];
-                }
+                for (int j = 0; j < 4; ++j)
+                    if (col + j < p.N) crow[col + j] = acc[i][h * 4 + j];
             }
         }
-    };
-    write_tile(p.splits == 1 ? p.C + (int64_t)z * MN : p.part + ((int64_t)sp * p.batch + z) * MN);
-    if (p.splits > 1 && arrived_last(p, z)) reduce_tile<T>(p, z, m0, n0, vec_out);
+    }
+}
+
+// Adds the split-K partials in split order: C = ((P0 + P1) + P2) + ...
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, float* __restrict__ C,
+                                                            int64_t count, int splits) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        float v = part[i];
+        for (int s = 1; s < splits; ++s) v = fadd(v, part[(int64_t)s * count + i]);
+        C[i] = v;
+    }
 }
 
 template <int MODE, class T>
@@ -441,30 +417,36 @@ Plan plan_for(int64_t batch, int64_t M, int64_t N, int64_t K, int split_request)
     const int64_t sms = sm_count();
     const int64_t tiles = batch * ((M + T::BM - 1) / T::BM) * ((N + T::BN - 1) / T::BN);
     const int64_t slabs = (K + T::BK - 1) / T::BK;
-    int64_t s = split_request;
-    if (s == 0) {                                            // automatic
-        const int64_t slots = sms * T::kCtasPerSm;
-        s = 1;
-        if (tiles * 2 <= slots && slabs >= 8) {              // less than half a wave of tiles
-            s = slots / tiles;
-            if (s > slabs / 4) s = slabs / 4;                // keep at least four slabs per range
-            if (s > 64) s = 64;
-            if (s < 1) s = 1;
-        }
-    }
-    if (s > slabs) s = slabs;
-    const int64_t chunk_slabs = (slabs + s - 1) / s;
-    s = (slabs + chunk_slabs - 1) / chunk_slabs;             // drop ranges that would be empty
-    const int64_t ctas = tiles * s;
-    const int64_t per_sm = (ctas + sms - 1) / sms;
-    const double warps = (double)(per_sm < T::kCtasPerSm ? per_sm : T::kCtasPerSm) * (T::kThreads / 32);
-    const double util = warps >= 12.0 ? 1.0 : warps / 12.0;
-    const double staging = T::BM >= 128 ? 1.0 : 1.06;        // the small tile stages twice the bytes per MAC
+    const int64_t slots = sms * T::kCtasPerSm;
+    // cost of cutting K into s ranges, in multiply-accumulates per SM at full issue rate
+    auto cost_of = [&](int64_t s, int64_t* actual) {
+        if (s > slabs) s = slabs;
+        const int64_t chunk_slabs = (slabs + s - 1) / s;
+        s = (slabs + chunk_slabs - 1) / chunk_slabs;         // drop ranges that would be empty
+        *actual = s;
+        const int64_t per_sm = (tiles * s + sms - 1) / sms;
+        const double warps = (double)(per_sm < T::kCtasPerSm ? per_sm : T::kCtasPerSm) * (T::kThreads / 32);
+        // measured: 16 resident warps per SM saturate the issue slots, 8 reach about 80 % of that
+        const double util = warps >= 16.0 ? 1.0 : (warps >= 8.0 ? 0.6 + 0.025 * warps : warps / 10.0);
+        const double staging = T::BM >= 128 ? 1.0 : 1.06;    // the small tile stages twice the bytes per MAC
+        return (double)per_sm * T::BM * T::BN * (double)(chunk_slabs * T::BK) / util * staging +
+               (s > 1 ? 1.1e6 : 0.0);                         // the reduction pass and its launch (~12 us)
+    };
     Plan pl;
     pl.small = T::BM < 128;
-    pl.splits = (int)s;
-    pl.cost = (double)per_sm * T::BM * T::BN * (double)(chunk_slabs * T::BK) / util * staging +
-              (s > 1 ? 2.0e6 : 0.0);                          // the reduction pass and its launch
+    int64_t s = split_request > 0 ? split_request : 1, actual = 1;
+    pl.cost = cost_of(s, &actual);
+    pl.splits = (int)actual;
+    if (split_request == 0 && tiles < slots && slabs >= 8) {  // automatic: try to fill the SMs
+        int64_t want = slots / tiles;
+        if (want > slabs / 4) want = slabs / 4;              // keep at least four slabs per range
+        if (want > 64) want = 64;
+        for (int64_t cand = 2; cand <= want; cand = cand < 4 ? cand + 1 : cand * 2 > want && cand != want ? want : cand * 2) {
+            int64_t got = 1;
+            const double c = cost_of(cand, &got);
+            if (c < pl.cost) { pl.cost = c; pl.splits = (int)got; }
+        }
+    }
     return pl;
 }
 
@@ -479,20 +461,9 @@ Plan make_plan(int mode, int64_t batch, int64_t M, int64_t N, int64_t K, int spl
     return small.cost < large.cost ? small : large;
 }
 
-// Split-K scratch: arrival counters (one int per output tile of the finest tiling, rounded up to
-// 256 bytes) followed by the partial sums.
-size_t counter_bytes(int64_t batch, int64_t M, int64_t N) {
-    const size_t tiles = (size_t)batch * (size_t)((M + TileSmall::BM - 1) / TileSmall::BM) *
-                         (size_t)((N + TileSmall::BN - 1) / TileSmall::BN);
-    return (tiles * sizeof(int) + 255) & ~(size_t)255;
-}
-
-size_t scratch_bytes(int64_t batch, int64_t M, int64_t N, int splits) {
-    return counter_bytes(batch, M, N) + (size_t)splits * (size_t)batch * (size_t)M * (size_t)N * sizeof(float);
-}
-
-bool workspace_ok(const void* ws, size_t bytes, int64_t batch, int64_t M, int64_t N, int splits) {
-    return ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255u) == 0 && bytes >= scratch_bytes(batch, M, N, splits);
+bool workspace_ok(const void* ws, size_t bytes, int splits, int64_t count) {
+    return ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255u) == 0 &&
+           bytes >= (size_t)splits * (size_t)count * sizeof(float);
 }
 
 int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspace, size_t workspace_bytes,
@@ -505,22 +476,14 @@ int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspa
     }
     if (split_k < 0) return PAMK_ERR_ARG;
     Plan pl = make_plan(mode, p.batch, p.M, p.N, p.K, split_k);
-    if (pl.splits > 1 && !workspace_ok(workspace, workspace_bytes, p.batch, p.M, p.N, pl.splits)) {
+    if (pl.splits > 1 && !workspace_ok(workspace, workspace_bytes, pl.splits, count)) {
         if (split_k != 0) return PAMK_ERR_WORKSPACE;         // an explicit split needs its scratch
         pl = make_plan(mode, p.batch, p.M, p.N, p.K, 1);     // automatic: fall back to no split
     }
     const int bm = pl.small ? TileSmall::BM : TileLarge::BM, bn = pl.small ? TileSmall::BN : TileLarge::BN;
     const int bk = pl.small ? TileSmall::BK : TileLarge::BK;
-    p.part = p.C;
-    p.counters = nullptr;
-    if (pl.splits > 1) {
-        const size_t cb = counter_bytes(p.batch, p.M, p.N);
-        p.counters = static_cast<int*>(workspace);
-        p.part = reinterpret_cast<float*>(static_cast<char*>(workspace) + cb);
-        // the counters must read zero when the first range arrives
-        const cudaError_t e = cudaMemsetAsync(workspace, 0, cb, st);
-        if (e != cudaSuccess) return record_cuda_error(e);
-    }
+    float* out = p.C;
+    if (pl.splits > 1) p.C = static_cast<float*>(workspace);
     const int slabs_total = (p.K + bk - 1) / bk;
     p.splits = pl.splits;
     p.k_chunk = ((slabs_total + pl.splits - 1) / pl.splits) * bk;
@@ -529,14 +492,22 @@ int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspa
     if (gy > 65535 || gz > 65535) return PAMK_ERR_SIZE;
     const dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)gz);
     const bool vec = vectorisable(p.A, a_kc, p.M, p.K) && vectorisable(p.B, b_kc, p.N, p.K);
+    int rc;
     switch (mode) {
         case kPam:
-            return pl.small ? dispatch<kPam, TileSmall>(p, a_kc, b_kc, vec, grid, st)
-                            : dispatch<kPam, TileLarge>(p, a_kc, b_kc, vec, grid, st);
-        case kStd: return dispatch<kStd, TileLarge>(p, a_kc, b_kc, vec, grid, st);
-        case kBwdL: return dispatch<kBwdL, TileLarge>(p, a_kc, b_kc, vec, grid, st);
-        default: return dispatch<kBwdR, TileLarge>(p, a_kc, b_kc, vec, grid, st);
+            rc = pl.small ? dispatch<kPam, TileSmall>(p, a_kc, b_kc, vec, grid, st)
+                          : dispatch<kPam, TileLarge>(p, a_kc, b_kc, vec, grid, st);
+            break;
+        case kStd: rc = dispatch<kStd, TileLarge>(p, a_kc, b_kc, vec, grid, st); break;
+        case kBwdL: rc = dispatch<kBwdL, TileLarge>(p, a_kc, b_kc, vec, grid, st); break;
+        default: rc = dispatch<kBwdR, TileLarge>(p, a_kc, b_kc, vec, grid, st); break;
     }
+    if (rc != PAMK_OK || pl.splits == 1) return rc;
+    const int64_t blocks = (count + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    splitk_reduce_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, st>>>(
+        static_cast<const float*>(workspace), out, count, pl.splits);
+    return check_launch();
 }
 
 // Validates one operand and reports whether it is contiguous along k.
@@ -587,7 +558,7 @@ extern "C" {
 
 size_t pamk_matmul_workspace_bytes(int64_t batch, int64_t M, int64_t N, int split_k) {
     if (split_k <= 1 || batch <= 0 || M <= 0 || N <= 0) return 0;
-    return scratch_bytes(batch, M, N, split_k);
+    return (size_t)split_k * (size_t)batch * (size_t)M * (size_t)N * sizeof(float);
 }
 
 int pamk_matmul_set_tile_policy(int policy) {
@@ -640,10 +611,8 @@ int pamk_matmul_static_scratch(const float* A, const float* B, float* C,
     if (split_k < 1) return PAMK_ERR_ARG;
     if (batch == 0 || M == 0 || N == 0) return PAMK_OK;
     if (C == nullptr) return PAMK_ERR_ARG;
-    // the partial sums and the per-tile arrival counters must fit in the fixed array
-    if ((double)split_k * (double)batch * (double)M * (double)N * sizeof(float) + (double)counter_bytes(batch, M, N) >
-        (double)(kStaticScratchFloats * sizeof(float)))
-        return PAMK_ERR_SIZE;
+    // every partial sum must fit in the fixed array
+    if ((double)split_k * (double)batch * (double)M * (double)N > (double)kStaticScratchFloats) return PAMK_ERR_SIZE;
     GemmParams p{};
     bool a_kc = true, b_kc = true;
     if (K > 0) {

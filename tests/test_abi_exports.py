@@ -39,5 +39,4 @@ def test_argument_checks_need_no_gpu():
     assert h.pamk_matmul(0, ptr, ptr, ptr, 1, 4, 4, 4, 0, 8, 2, 0, 4, 1, 1.0, 1, None, 0, None) == -3
     assert h.pamk_matmul(0, ptr, ptr, ptr, 1, 2**31, 4, 4, 0, 4, 1, 0, 4, 1, 1.0, 1, None, 0, None) == -2
     assert h.pamk_matmul(0, ptr, ptr, ptr, 1, 4, 4, 64, 0, 64, 1, 0, 4, 1, 1.0, 4, None, 0, None) == -4
-    # partial sums plus one 256-byte block of per-tile arrival counters
-    assert h.pamk_matmul_workspace_bytes(2, 3, 5, 4) == 256 + 2 * 3 * 5 * 4 * 4
+    assert h.pamk_matmul_workspace_bytes(2, 3, 5, 4) == 2 * 3 * 5 * 4 * 4
