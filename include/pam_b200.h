@@ -170,6 +170,27 @@ int pamk_layer_norm_bwd(const float* x, const float* weight, const float* dy, fl
                         float* dweight, float* dbias, int64_t rows, int64_t width, float eps, float offset,
                         int approx_bwd, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- fused softmax / logsumexp over the last dimension ----------------------------------------------
+ * Replace the launch chains of pam_ops.softmax (pam/pam_ops.py:305-328) and pam_ops.logsumexp
+ * (:331-342) and of their autograd:
+ *   s = pam(x, log2 e) (-inf stays -inf);  shift = floor(max of s over the WHOLE tensor);
+ *   e = exp2_op(s - shift) (0 where x = -inf);  softmax = pad(e, row sum of e);
+ *   logsumexp = pad(shift + log2_op(row sum of e), log2 e)   [that log2 always with offset 1].
+ * x, y, dy, dx are [rows, len] contiguous (logsumexp: y and dy are [rows]); len <=
+ * pamk_softmax_max_len().  Every call first reduces the whole-tensor maximum into `workspace`
+ * (pamk_softmax_workspace_bytes(rows, len) bytes, 16-byte aligned), also in the backward calls,
+ * which recompute the forward chain from x. */
+int pamk_softmax_max_len(void);
+size_t pamk_softmax_workspace_bytes(int64_t rows, int64_t len);
+int pamk_softmax_fwd(const float* x, float* y, int64_t rows, int64_t len, float offset,
+                     void* workspace, size_t workspace_bytes, void* stream);
+int pamk_softmax_bwd(const float* x, const float* dy, float* dx, int64_t rows, int64_t len, float offset,
+                     int approx_bwd, void* workspace, size_t workspace_bytes, void* stream);
+int pamk_logsumexp_fwd(const float* x, float* y, int64_t rows, int64_t len, float offset,
+                       void* workspace, size_t workspace_bytes, void* stream);
+int pamk_logsumexp_bwd(const float* x, const float* dy, float* dx, int64_t rows, int64_t len, float offset,
+                       int approx_bwd, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- fused PAM Adam ------------------------------------------------------------------------------
  * Replaces the per-tensor launch chain of the reference's PAM Adam
  * (submodules/fairseq/fairseq/optim/adam.py:226-252 over pam.mul / pam.div / pam.pow):

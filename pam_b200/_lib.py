@@ -45,6 +45,12 @@ _SIGNATURES = {
     "pamk_layer_norm_fwd": (_i, [_p, _p, _p, _p, _i64, _i64, _f, _f, _p]),
     "pamk_layer_norm_bwd_workspace_bytes": (_sz, [_i64, _i64]),
     "pamk_layer_norm_bwd": (_i, [_p] * 6 + [_i64, _i64, _f, _f, _i, _p, _sz, _p]),
+    "pamk_softmax_max_len": (_i, []),
+    "pamk_softmax_workspace_bytes": (_sz, [_i64, _i64]),
+    "pamk_softmax_fwd": (_i, [_p, _p, _i64, _i64, _f, _p, _sz, _p]),
+    "pamk_softmax_bwd": (_i, [_p, _p, _p, _i64, _i64, _f, _i, _p, _sz, _p]),
+    "pamk_logsumexp_fwd": (_i, [_p, _p, _i64, _i64, _f, _p, _sz, _p]),
+    "pamk_logsumexp_bwd": (_i, [_p, _p, _p, _i64, _i64, _f, _i, _p, _sz, _p]),
     "pamk_adam_step": (_i, [_p, _p, _p, _p, _p, _i] + [_f] * 8 + [_p]),
     "pamk_issue_rate": (_i, [_i, _i, _i, _p, ctypes.POINTER(_f), ctypes.POINTER(ctypes.c_double), _p]),
 }

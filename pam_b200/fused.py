@@ -98,8 +98,78 @@ def layer_norm(x, normalized_shape, weight, bias, eps, *, offset=None, approx_bw
 
 # ---- softmax ---------------------------------------------------------------------------------------
 
-def softmax_supported(x, dim):
-    return False
+_MAX_ROW = 12288
+
+
+def _last_dim(x, dim):
+    return isinstance(dim, int) and x.dim() > 0 and dim in (-1, x.dim() - 1)
+
+
+def softmax_supported(x, dim, approx_bwd=False):
+    return (enabled and isinstance(x, torch.Tensor) and x.is_cuda and x.dtype == torch.float32 and
+            _last_dim(x, dim) and 0 < x.shape[-1] <= _MAX_ROW and x.numel() > 0 and _uniform(approx_bwd))
+
+
+def _rows(handle, name, x2, extra, out, offset, approx=None):
+    dev = x2.device
+    rows, length = x2.shape
+    ws_bytes = handle.pamk_softmax_workspace_bytes(rows, length)
+    ws = _workspace(dev, ws_bytes)
+    args = [x2.data_ptr()] + [t.data_ptr() for t in extra] + [out.data_ptr(), rows, length, offset]
+    if approx is not None:
+        args.append(int(bool(approx)))
+    with _lib.device_guard(dev):
+        status = getattr(handle, name)(*args, ws.data_ptr(), ws_bytes, _lib.stream_ptr(dev))
+    _lib.check(status, name)
+    return out
+
+
+class _Softmax(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, offset, approx):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        ctx.save_for_backward(x2)
+        ctx.cfg = (offset, approx, x.shape)
+        return _rows(_lib.lib(), "pamk_softmax_fwd", x2, [], torch.empty_like(x2), offset).view(x.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        (x2,) = ctx.saved_tensors
+        offset, approx, shape = ctx.cfg
+        g2 = g.reshape(x2.shape).contiguous()
+        dx = _rows(_lib.lib(), "pamk_softmax_bwd", x2, [g2], torch.empty_like(x2), offset, approx)
+        return dx.view(shape), None, None
+
+
+class _LogSumExp(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, offset, approx):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        ctx.save_for_backward(x2)
+        ctx.cfg = (offset, approx, x.shape)
+        out = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+        return _rows(_lib.lib(), "pamk_logsumexp_fwd", x2, [], out, offset).view(x.shape[:-1])
+
+    @staticmethod
+    def backward(ctx, g):
+        (x2,) = ctx.saved_tensors
+        offset, approx, shape = ctx.cfg
+        g1 = g.reshape(-1).contiguous()
+        dx = _rows(_lib.lib(), "pamk_logsumexp_bwd", x2, [g1], torch.empty_like(x2), offset, approx)
+        return dx.view(shape), None, None
+
+
+def _flag(approx_bwd):
+    return approx_bwd if isinstance(approx_bwd, bool) else bool(approx_bwd[0])
+
+
+def softmax(x, dim, *, offset=None, approx_bwd=False):
+    return _Softmax.apply(x, _offset(offset), _flag(approx_bwd))
+
+
+def logsumexp(x, dim, keepdim=False, *, offset=None, approx_bwd=False):
+    out = _LogSumExp.apply(x, _offset(offset), _flag(approx_bwd))
+    return out.unsqueeze(-1) if keepdim else out
 
 
 # ---- Adam --------------------------------------------------------------------------------------------

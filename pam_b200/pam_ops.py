@@ -210,7 +210,7 @@ def softmax(x, dim=None, *, offset=None, approx_bwd=False, use_kernel=True):
     """PAM softmax (pam/pam_ops.py:305-328): x*log2(e) by PAM, exp2 by the piecewise affine
     exponential after subtracting floor(max) of the WHOLE tensor, -inf entries (attention masks)
     forced to probability 0, ordinary sum, PAM division."""
-    if fused.softmax_supported(x, dim):
+    if fused.softmax_supported(x, dim, approx_bwd):
         return fused.softmax(x, dim, offset=offset, approx_bwd=approx_bwd)
     kw = dict(offset=offset, approx_bwd=approx_bwd)
     masked = x == float("-inf")
@@ -224,6 +224,10 @@ def softmax(x, dim=None, *, offset=None, approx_bwd=False, use_kernel=True):
 def logsumexp(x, dim, keepdim=False, *, offset=None, approx_bwd=False, use_kernel=True):
     """pam/pam_ops.py:331-342.  As in the reference, the log2 of the row sums runs with the
     default offset and the exact backward whatever this call's settings are."""
+    if fused.softmax_supported(x, dim, approx_bwd):
+        # the fused route skips the reference's `assert x.isfinite().all()`, which would stall the
+        # stream on a device-to-host read; non-finite inputs give NaN there
+        return fused.logsumexp(x, dim, keepdim, offset=offset, approx_bwd=approx_bwd)
     kw = dict(offset=offset, approx_bwd=approx_bwd)
     assert x.isfinite().all()
     scaled = mul(x, _LOG2E, **kw)

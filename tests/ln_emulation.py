@@ -77,6 +77,54 @@ class Chain:
         return y, dc + d_s1, dw, db
 
 
+    # ---- softmax / logsumexp over the last dimension (pam_b200/csrc/softmax.cu) -------------------
+    def _scaled(self, x):
+        log2e = _f(math.log2(math.e))
+        masked = x == float("-inf")
+        scaled = torch.where(masked, torch.full_like(x, float("-inf")), self.mul(x, log2e))
+        return masked, scaled, torch.floor(torch.max(scaled)), log2e
+
+    def softmax(self, x, g, approx):
+        K, off = self.K, self.off
+        n = x.shape[-1]
+        x, g = x.reshape(-1, n), g.reshape(-1, n)
+        ln2, one = _f(math.log(2.0)), _f(1.0)
+        masked, scaled, shift, log2e = self._scaled(x)
+        adj = scaled - shift
+        big = K.pa_exp_fwd(adj, 2.0, off)
+        e = torch.where(masked, torch.zeros_like(big), big)
+        total = self.rowsum(e)
+        y = self.div(e, total)
+        recip = self.div(one, total)
+        dden = -self.mul(self.div(self.div(e, total), total), g) if approx else self.div_bwd(e, total, g)
+        de = self.mul(recip, g) if approx else self.mul_bwd(e, recip, g, 1.0)
+        d_big = torch.where(masked, torch.zeros_like(de), de + self.rowsum(dden))
+        d_adj = self.mul(self.mul(e, ln2), d_big) if approx else K.pa_exp_bwd(adj, d_big, 2.0, off)
+        d_s = torch.where(masked, torch.zeros_like(d_adj), d_adj)
+        dx = self.mul(d_s, log2e) if approx else self.mul_bwd(x, log2e, d_s)
+        return y, dx
+
+    def logsumexp(self, x, g, approx):
+        """x [rows, n], g [rows]; the log2 of the row sum always runs with offset 1 and the exact
+        backward (pam_ops.py:341)."""
+        K, off = self.K, self.off
+        n = x.shape[-1]
+        x, g = x.reshape(-1, n), g.reshape(-1, 1)
+        ln2, one = _f(math.log(2.0)), _f(1.0)
+        _, scaled, shift, log2e = self._scaled(x)
+        adj = scaled - shift
+        e = K.pa_exp_fwd(adj, 2.0, off)
+        total = self.rowsum(e)
+        u = shift + K.pa_log_fwd(total, 2.0, 1.0)
+        y = self.div(u, log2e)
+        recip = self.div(one, log2e)
+        d_u = self.mul(recip, g) if approx else self.mul_bwd(u, recip, g, 1.0)
+        d_total = K.pa_log_bwd(total, d_u, 2.0, 1.0)
+        d_adj = self.mul(self.mul(e, ln2), d_total) if approx else K.pa_exp_bwd(adj, d_total.expand_as(adj).contiguous(), 2.0, off)
+        dx = self.mul(d_adj, log2e) if approx else self.mul_bwd(x, log2e, d_adj)
+        return y.reshape(-1), dx
+
+
 def torch_rowsum(t):
     return t.sum(-1, keepdim=True)
 
@@ -85,23 +133,30 @@ def torch_colsum(t):
     return t.sum(0)
 
 
-def kernel_rowsum(vec):
-    """Summation order of the kernel: lane L holds the columns (q*32 + L)*vec + j in the order
-    (q, j), adds them one by one starting from +0, then the 32 lane sums are joined by a
-    butterfly (xor 16, 8, 4, 2, 1)."""
+def kernel_rowsum(vec, warps=1):
+    """Summation order of the row kernels: thread t of a group of warps*32 holds the columns
+    (q*group + t)*vec + j in the order (q, j) and adds them one by one starting from +0; the 32
+    lane sums of each warp are joined by a butterfly (xor 16, 8, 4, 2, 1); the warp sums, if there
+    is more than one warp, are added in warp order."""
+    group = 32 * warps
+
     def rowsum(t):
         rows, n = t.shape
-        chunks = -(-n // (32 * vec))
-        padded = torch.zeros(rows, chunks * 32 * vec)
+        chunks = -(-n // (group * vec))
+        padded = torch.zeros(rows, chunks * group * vec)
         padded[:, :n] = t
-        lanes = padded.view(rows, chunks, 32, vec).permute(0, 2, 1, 3).reshape(rows, 32, chunks * vec)
-        part = torch.zeros(rows, 32)
+        lanes = padded.view(rows, chunks, group, vec).permute(0, 2, 1, 3).reshape(rows, group, chunks * vec)
+        part = torch.zeros(rows, group)
         for i in range(chunks * vec):
             part = part + lanes[:, :, i]
+        part = part.view(rows, warps, 32)
         idx = torch.arange(32)
         for d in (16, 8, 4, 2, 1):
-            part = part + part[:, idx ^ d]
-        return part[:, :1].contiguous()
+            part = part + part[:, :, idx ^ d]
+        total = part[:, 0, 0]
+        for wdx in range(1, warps):
+            total = total + part[:, wdx, 0]
+        return total.reshape(rows, 1).contiguous()
     return rowsum
 
 

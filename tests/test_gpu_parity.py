@@ -482,6 +482,82 @@ def test_layer_norm_config2_rows(pam, dev):
     assert_close_nan(ln.bias.grad, gy.sum(0), 1e-4, 1e-3, "db")
 
 
+# ---- fused softmax / logsumexp -----------------------------------------------------------------------
+
+def _row_order(length):
+    """(vec, warps) of the row kernel the library picks for contiguous, 16-byte aligned rows."""
+    vec = 4 if length % 4 == 0 else 1
+    return vec, (1 if length <= 1024 else 8)
+
+
+@pytest.mark.parametrize("length", [1, 5, 32, 197, 200, 1000, 1024, 1028, 4096, 10000])
+@pytest.mark.parametrize("approx", [True, False])
+def test_fused_softmax_logsumexp_bit_exact_against_replayed_chain(pam, dev, length, approx):
+    import ln_emulation as E
+    g = torch.Generator().manual_seed(length)
+    rows = 9
+    for offset in (None, 1.0552):
+        x = torch.randn(rows, length, generator=g) * 3
+        gy = torch.randn(rows, length, generator=g)
+        chain = E.Chain(offset, E.kernel_rowsum(*_row_order(length)), E.torch_colsum)
+        # softmax with attention-style masking (-inf) in some rows
+        xm = x.clone()
+        if length > 2:
+            xm[::2, -(length // 3 + 1):] = float("-inf")
+        xd = xm.to(dev).requires_grad_()
+        y = pam.softmax(xd, dim=-1, offset=offset, approx_bwd=approx)
+        y.backward(gy.to(dev))
+        wy, wdx = chain.softmax(xm, gy, approx)
+        assert_bits_equal(y, wy, f"softmax len={length}")
+        assert_bits_equal(xd.grad, wdx, f"softmax dx len={length}")
+        # logsumexp and log_softmax (finite inputs)
+        xd = x.to(dev).requires_grad_()
+        z = pam.logsumexp(xd, dim=-1, offset=offset, approx_bwd=approx)
+        z.backward(gy[:, 0].to(dev))
+        wz, wdz = chain.logsumexp(x, gy[:, 0], approx)
+        assert_bits_equal(z, wz, f"logsumexp len={length}")
+        assert_bits_equal(xd.grad, wdz, f"logsumexp dx len={length}")
+
+
+def test_fused_softmax_shift_is_global_and_nan_is_sticky(pam, dev):
+    import ln_emulation as E
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(3000, 64, generator=g)
+    x[2999, 63] = 40.0                       # the maximum sits in the last row: every row's shift moves
+    y = pam.softmax(x.to(dev), dim=-1)
+    wy, _ = E.Chain(None, E.kernel_rowsum(4, 1), E.torch_colsum).softmax(x, torch.zeros_like(x), True)
+    assert_bits_equal(y, wy)
+    # a fully masked row is NaN (0 / 0 through PAM division), the others are untouched
+    xm = x.clone()
+    xm[7] = float("-inf")
+    ym = pam.softmax(xm.to(dev), dim=-1).cpu()
+    assert ym[7].isnan().all() and torch.equal(ym[8], wy[8])
+    # +inf or NaN anywhere poisons the whole-tensor shift, as with torch.max in the reference
+    xn = x.clone()
+    xn[5, 5] = float("nan")
+    assert pam.softmax(xn.to(dev), dim=-1).isnan().all()
+
+
+def test_fused_softmax_matches_unfused_route(pam, dev):
+    from pam_b200 import fused
+    g = torch.Generator().manual_seed(6)
+    x = (torch.randn(12, 197, 197, generator=g) * 2).to(dev)        # DeiT attention scores, one layer / 4 images
+    gy = torch.randn(12, 197, 197, generator=g).to(dev)
+    outs = []
+    for flag in (True, False):
+        fused.enabled = flag
+        try:
+            xi = x.clone().requires_grad_()
+            y = pam.softmax(xi, dim=-1, approx_bwd=True)
+            y.backward(gy)
+            z = pam.log_softmax(xi, dim=-1, approx_bwd=True)
+            outs.append((y.detach(), xi.grad.clone(), z.detach()))
+        finally:
+            fused.enabled = True
+    for name, a, b in zip(("y", "dx", "log_softmax"), *outs):
+        assert_close_nan(a, b, 1e-4, 1e-5 * float(b.abs().max()) + 1e-7, name)
+
+
 # ---- fused Adam ---------------------------------------------------------------------------------------
 
 def test_fused_adam_many_tensors_bit_exact(pam, oracle, dev):

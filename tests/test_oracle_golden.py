@@ -183,3 +183,25 @@ def test_fused_layer_norm_chain_equals_reference(oracle, golden, oname, mode):
     y, dx, _, _ = chain.run(golden["ln/x"], None, None, golden["ln/g"], 1e-6, approx)
     assert_bits_equal(y.view(7, 3, 48), golden[f"ln/plain/{k}/y"])
     assert_bits_equal(dx.view(7, 3, 48), golden[f"ln/plain/{k}/dx"])
+
+
+@pytest.mark.parametrize("oname,mode", CASES_EW)
+def test_fused_softmax_chain_equals_reference(oracle, golden, oname, mode):
+    """The chains that the fused softmax / logsumexp kernels evaluate, summed with torch.sum, are the
+    reference's softmax, logsumexp and log_softmax forward and backward bit for bit."""
+    import ln_emulation as E
+    chain = E.Chain(None if oname == "none" else 1.0552, E.torch_rowsum, E.torch_colsum)
+    approx = mode == "approx"
+    k = f"{oname}/{mode}"
+    g = golden["sm/g"]
+    for name, xin in (("softmax", "sm/x"), ("softmax_masked", "sm/x_masked")):
+        y, dx = chain.softmax(golden[xin], g, approx)
+        assert_bits_equal(y.view(6, 5, 11), golden[f"sm/{name}/{k}/y"], name)
+        assert_bits_equal(dx.view(6, 5, 11), golden[f"sm/{name}/{k}/dx"], name + "/dx")
+    y, dx = chain.logsumexp(golden["sm/x"], g[..., 0], approx)
+    assert_bits_equal(y.view(6, 5), golden[f"sm/logsumexp/{k}/y"], "logsumexp")
+    assert_bits_equal(dx.view(6, 5, 11), golden[f"sm/logsumexp/{k}/dx"], "logsumexp/dx")
+    # log_softmax = x - logsumexp(keepdim): its gradient is g - d(logsumexp)(sum of g over the row)
+    y, dlse = chain.logsumexp(golden["sm/x"], -g.sum(-1), approx)
+    assert_bits_equal(golden["sm/x"] - y.view(6, 5, 1), golden[f"sm/log_softmax/{k}/y"], "log_softmax")
+    assert_bits_equal(g + dlse.view(6, 5, 11), golden[f"sm/log_softmax/{k}/dx"], "log_softmax/dx")
