@@ -206,39 +206,77 @@ def run_ours(args):
     scratch = torch.zeros(4, dtype=torch.int32, device=dev)
     for name, variant in (("fadd", 0), ("iadd", 1), ("iadd_fadd", 2), ("imad_fadd", 3), ("mixed_fadd", 4)):
         ms, steps_done = ctypes.c_float(), ctypes.c_double()
-        _lib.check(lib.pamk_issue_rate(variant, 20000, 4, scratch.data_ptr(), ctypes.byref(ms), ctypes.byref(steps_done),
+        _lib.check(lib.pamk_issue_rate(variant, 3000, 4, scratch.data_ptr(), ctypes.byref(ms), ctypes.byref(steps_done),
                                        torch.cuda.current_stream().cuda_stream), "issue_rate")
         peak[name] = steps_done.value / (ms.value * 1e-3)
     mac_peak = max(peak["iadd_fadd"], peak["imad_fadd"], peak["mixed_fadd"])
 
     # ---- e2e: host buffers in, results out, through the public API ------------------------------------
+    # Copies are pipelined against the compute per layer on two extra streams (PCIe is full duplex):
+    # inputs of layer i+1 upload and results of layer i-1 download while layer i computes.
     host = make_inputs(1234 + rank, pin=True)
     h2d = sum(t.numel() * 4 for v in host.values() for t in (v if isinstance(v, list) else [v]))
-    out_host = None
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    main = torch.cuda.current_stream(dev)
+    out_host = {}
+
+    def download(key, tensors):
+        ready = torch.cuda.Event()
+        ready.record(main)
+        s_out.wait_event(ready)
+        with torch.cuda.stream(s_out):
+            for j, t in enumerate(tensors):
+                slot = out_host.get((key, j))
+                if slot is None:
+                    slot = out_host[(key, j)] = torch.empty(t.shape, dtype=t.dtype).pin_memory()
+                slot.copy_(t, non_blocking=True)
+                t.record_stream(s_out)
+
+    def e2e_step():
+        uploads = []
+        with torch.cuda.stream(s_in):
+            for i in range(len(LAYERS)):
+                trio = [host[k][i].to(dev, non_blocking=True) for k in ("X", "W", "G")]
+                ev = torch.cuda.Event()
+                ev.record(s_in)
+                uploads.append((trio, ev))
+            ln_in = [host["LNX"].to(dev, non_blocking=True), host["LNG"].to(dev, non_blocking=True)]
+            ln_ev = torch.cuda.Event()
+            ln_ev.record(s_in)
+        for i, ((X, W, G), ev) in enumerate(uploads):
+            main.wait_event(ev)
+            for t in (X, W, G):
+                t.record_stream(main)
+            X.requires_grad_()
+            W.requires_grad_()
+            Y = pam.linear(X, W, approx_bwd=True)
+            Y.backward(G)
+            download(i, [Y.detach(), X.grad, W.grad])
+        main.wait_event(ln_ev)
+        x = ln_in[0].requires_grad_()
+        for t in ln_in:
+            t.record_stream(main)
+        y = ln(x)
+        y.backward(ln_in[1])
+        ln.weight.grad = ln.bias.grad = None
+        download("ln", [y.detach(), x.grad])
+        main.wait_stream(s_out)
+
     e2e_ms = 0.0
     e2e_steps = max(3, min(args.steps, 10))
-    d2h = 0
     for it in range(2 + e2e_steps):
         barrier()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
-        on_dev = {k: [t.to(dev, non_blocking=True) for t in v] if isinstance(v, list) else v.to(dev, non_blocking=True)
-                  for k, v in host.items()}
-        outs = step(on_dev, keep=True)
-        if out_host is None:
-            out_host = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
-            d2h = sum(o.numel() * 4 for o in outs)
-        for dst, src in zip(out_host, outs):
-            dst.copy_(src, non_blocking=True)
+        e2e_step()
         t1.record()
         torch.cuda.synchronize()
         if it >= 2:
             e2e_ms += t0.elapsed_time(t1)
+    d2h = sum(t.numel() * 4 for t in out_host.values())
 
-    times = torch.tensor([total_ms, e2e_ms, gemm_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, gemm_ms_max = times.tolist()
+    from pam_b200 import parallel
+    total_ms, e2e_ms = (parallel.max_over_ranks(v, dev) for v in (total_ms, e2e_ms))
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -256,7 +294,8 @@ def run_ours(args):
                        "sharding": "per-GPU replica of the workload on its own rows; no collective"},
             "e2e": {"value": world * MACS_PER_STEP * e2e_steps / (e2e_ms * 1e-3), "unit": "MAC/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "note": "pinned host inputs -> device -> pam.linear/LayerNorm fwd+bwd -> all outputs and gradients back to pinned host"},
+                    "note": "pinned host inputs -> device -> pam.linear/LayerNorm fwd+bwd -> all outputs and gradients "
+                            "back to pinned host; uploads and downloads overlap the compute on their own streams"},
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
             "roofline": {"bound": "issue (INT32 add + FP32 add per MAC)", "achieved": gemm_rate / 1e12, "peak": mac_peak / 1e12,
