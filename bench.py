@@ -206,7 +206,7 @@ def run_ours(args):
     scratch = torch.zeros(4, dtype=torch.int32, device=dev)
     for name, variant in (("fadd", 0), ("iadd", 1), ("iadd_fadd", 2), ("imad_fadd", 3), ("mixed_fadd", 4)):
         ms, steps_done = ctypes.c_float(), ctypes.c_double()
-        _lib.check(lib.pamk_issue_rate(variant, 3000, 4, scratch.data_ptr(), ctypes.byref(ms), ctypes.byref(steps_done),
+        _lib.check(lib.pamk_issue_rate(variant, 8000, 4, scratch.data_ptr(), ctypes.byref(ms), ctypes.byref(steps_done),
                                        torch.cuda.current_stream().cuda_stream), "issue_rate")
         peak[name] = steps_done.value / (ms.value * 1e-3)
     mac_peak = max(peak["iadd_fadd"], peak["imad_fadd"], peak["mixed_fadd"])

@@ -91,7 +91,7 @@ int pamk_issue_rate(int variant, int iters, int ctas_per_sm, int* scratch, float
     if (err != cudaSuccess) { cudaEventDestroy(e0); return record_cuda_error(err); }
     void (*fn[7])(int*, int, int, cudaStream_t) = {launch<0>, launch<1>, launch<2>, launch<3>,
                                                     launch<4>, launch<5>, launch<6>};
-    fn[variant](scratch, grid, iters / 8 + 1, st);   // warm-up
+    fn[variant](scratch, grid, iters, st);           // warm-up at full length: clocks settle under this load
     cudaEventRecord(e0, st);
     fn[variant](scratch, grid, iters, st);
     cudaEventRecord(e1, st);

@@ -30,6 +30,21 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// Divisors shared by every row of a launch: the row width n (both means) and log2f(2) = 1 (the
+// base-2 log kernel divides by it).  Prepared once per thread.
+struct Shared {
+    Divisor by_n, by_lb2;
+    float lb2;
+};
+
+__device__ __forceinline__ Shared make_shared(float nf, int32_t off) {
+    Shared s;
+    s.lb2 = log2f(2.0f);                            // the base-2 kernels scale by log2f(2) = 1
+    s.by_n = make_divisor(nf, off);
+    s.by_lb2 = make_divisor(s.lb2, off);
+    return s;
+}
+
 struct LnArgs {
     const float* x;
     const float* w;      // may be null
@@ -48,13 +63,12 @@ struct RowStats {
     float s1, mu, s2, v, l, m, e, denom;
 };
 
-__device__ __forceinline__ void finish_stats(RowStats& r, const LnArgs& a) {
-    const float lb2 = log2f(2.0f);                 // the base-2 kernels scale by log2f(2) = 1
-    const float var = div(r.s2, a.nf, a.off);
+__device__ __forceinline__ void finish_stats(RowStats& r, const LnArgs& a, const Shared& sh) {
+    const float var = div_by(r.s2, sh.by_n);
     r.v = fadd(var, a.eps);
-    r.l = log_base(r.v, lb2, a.off);
+    r.l = div_by(log2(r.v), sh.by_lb2);             // log_base(v, log2f(2), off)
     r.m = mul(r.l, 0.5f, a.off);
-    r.e = exp_base(r.m, lb2, a.off);
+    r.e = exp_base(r.m, sh.lb2, a.off);
     r.denom = r.v == 0.0f ? 0.0f : r.e;
 }
 
@@ -70,15 +84,19 @@ __device__ __forceinline__ void load_row(RowRegs<VEC, NCH>& r, const float* p, i
 #pragma unroll
     for (int q = 0; q < NCH; ++q) {
         const int col = (q * 32 + lane) * VEC;
-        if (VEC == 4) {
-            if (col < width) {
+        if (col < width) {
+            if (VEC == 4) {
                 const float4 t = __ldg(reinterpret_cast<const float4*>(p + col));
                 r.v[q * 4] = t.x; r.v[q * 4 + 1] = t.y; r.v[q * 4 + 2] = t.z; r.v[q * 4 + 3] = t.w;
+            } else if (VEC == 2) {
+                const float2 t = __ldg(reinterpret_cast<const float2*>(p + col));
+                r.v[q * 2] = t.x; r.v[q * 2 + 1] = t.y;
             } else {
-                r.v[q * 4] = r.v[q * 4 + 1] = r.v[q * 4 + 2] = r.v[q * 4 + 3] = fill;
+                r.v[q] = __ldg(p + col);
             }
         } else {
-            r.v[q] = col < width ? __ldg(p + col) : fill;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) r.v[q * VEC + j] = fill;
         }
     }
 }
@@ -91,6 +109,8 @@ __device__ __forceinline__ void store_row(const RowRegs<VEC, NCH>& r, float* p, 
         if (col < width) {
             if (VEC == 4)
                 *reinterpret_cast<float4*>(p + col) = make_float4(r.v[q * 4], r.v[q * 4 + 1], r.v[q * 4 + 2], r.v[q * 4 + 3]);
+            else if (VEC == 2)
+                *reinterpret_cast<float2*>(p + col) = make_float2(r.v[q * 2], r.v[q * 2 + 1]);
             else
                 p[col] = r.v[q];
         }
@@ -105,12 +125,13 @@ __device__ __forceinline__ bool live(int i, int width, int lane) {
 // Forward chain up to the centred row and the row scalars.  Padding lanes hold 0 in `c` so that
 // pam(0, 0) = +0 leaves the sums untouched.
 template <int VEC, int NCH>
-__device__ __forceinline__ void centre_and_stats(RowRegs<VEC, NCH>& c, RowStats& st, const LnArgs& a, int lane) {
+__device__ __forceinline__ void centre_and_stats(RowRegs<VEC, NCH>& c, RowStats& st, const LnArgs& a,
+                                                 const Shared& sh, int lane) {
     float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < NCH * VEC; ++i) s = fadd(s, c.v[i]);
     st.s1 = warp_sum(s);
-    st.mu = div(st.s1, a.nf, a.off);
+    st.mu = div_by(st.s1, sh.by_n);
     s = 0.0f;
 #pragma unroll
     for (int i = 0; i < NCH * VEC; ++i) {
@@ -118,7 +139,7 @@ __device__ __forceinline__ void centre_and_stats(RowRegs<VEC, NCH>& c, RowStats&
         s = fadd(s, mul(c.v[i], c.v[i], a.off));
     }
     st.s2 = warp_sum(s);
-    finish_stats(st, a);
+    finish_stats(st, a, sh);
 }
 
 template <int VEC, int NCH>
@@ -126,6 +147,7 @@ __global__ void __launch_bounds__(kThreads) ln_fwd_kernel(const LnArgs a) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
+    const Shared sh = make_shared(a.nf, a.off);
     RowRegs<VEC, NCH> w, b;
     if (a.w) load_row<VEC, NCH>(w, a.w, a.width, lane, 1.0f);
     if (a.b) load_row<VEC, NCH>(b, a.b, a.width, lane, 0.0f);
@@ -133,10 +155,11 @@ __global__ void __launch_bounds__(kThreads) ln_fwd_kernel(const LnArgs a) {
         RowRegs<VEC, NCH> c;
         load_row<VEC, NCH>(c, a.x + row * a.width, a.width, lane, 0.0f);
         RowStats st;
-        centre_and_stats<VEC, NCH>(c, st, a, lane);
+        centre_and_stats<VEC, NCH>(c, st, a, sh, lane);
+        const Divisor by_denom = make_divisor(st.denom, a.off);
 #pragma unroll
         for (int i = 0; i < NCH * VEC; ++i) {
-            float y = div(c.v[i], st.denom, a.off);
+            float y = div_by(c.v[i], by_denom);
             if (a.w) y = mul(y, w.v[i], a.off);
             if (a.b) y = fadd(y, b.v[i]);
             c.v[i] = y;
@@ -153,7 +176,8 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_kernel(const LnArgs a) {
     const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + wid;
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
     const float ln2 = 0.693147180559945309417f;      // float(math.log(2.0)), cuda_bindings.py:232,271
-    const float recip_n = div(1.0f, a.nf, a.off);
+    const Shared sh = make_shared(a.nf, a.off);
+    const float recip_n = div_by(1.0f, sh.by_n);
     RowRegs<VEC, NCH> w, dw, db;
     if (a.w) load_row<VEC, NCH>(w, a.w, a.width, lane, 1.0f);
 #pragma unroll
@@ -164,15 +188,16 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_kernel(const LnArgs a) {
         load_row<VEC, NCH>(c, a.x + row * a.width, a.width, lane, 0.0f);
         load_row<VEC, NCH>(g, a.dy + row * a.width, a.width, lane, 0.0f);
         RowStats st;
-        centre_and_stats<VEC, NCH>(c, st, a, lane);
-        const float recip = div(1.0f, st.denom, a.off);
+        centre_and_stats<VEC, NCH>(c, st, a, sh, lane);
+        const Divisor by_denom = make_divisor(st.denom, a.off);
+        const float recip = div_by(1.0f, by_denom);
 
         // d(out)/d(xn), the division's two gradients; g is overwritten by d_c1
         float sum_dden = 0.0f;
 #pragma unroll
         for (int i = 0; i < NCH * VEC; ++i) {
             const bool on = live<VEC, NCH>(i, a.width, lane);
-            const float xn = div(c.v[i], st.denom, a.off);
+            const float xn = div_by(c.v[i], by_denom);
             float dxn = g.v[i];
             if (a.w) {
                 if (on) {
@@ -183,7 +208,7 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_kernel(const LnArgs a) {
             } else if (a.partials && on) {
                 db.v[i] = fadd(db.v[i], g.v[i]);
             }
-            const float dden = APPROX ? -mul(div(xn, st.denom, a.off), dxn, a.off)
+            const float dden = APPROX ? -mul(div_by(xn, by_denom), dxn, a.off)
                                       : div_bwd(c.v[i], st.denom, dxn, a.off);
             if (on) sum_dden = fadd(sum_dden, dden);
             g.v[i] = APPROX ? mul(recip, dxn, a.off) : mul_bwd(c.v[i], recip, dxn, 0);
@@ -191,11 +216,10 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_kernel(const LnArgs a) {
         const float d_denom = warp_sum(sum_dden);
 
         // scalar chain back through pow(v, 0.5) and the variance
-        const float lb2 = log2f(2.0f);
         const float d_e = st.v == 0.0f ? 0.0f : d_denom;
-        const float d_m = APPROX ? mul(mul(st.e, ln2, a.off), d_e, a.off) : exp_base_bwd(st.m, d_e, lb2, a.off);
+        const float d_m = APPROX ? mul(mul(st.e, ln2, a.off), d_e, a.off) : exp_base_bwd(st.m, d_e, sh.lb2, a.off);
         const float d_l = APPROX ? mul(d_m, 0.5f, a.off) : mul_bwd(st.l, 0.5f, d_m, a.off);
-        const float d_v = APPROX ? div(div(d_l, st.v, a.off), ln2, a.off) : log_base_bwd(st.v, d_l, lb2, a.off);
+        const float d_v = APPROX ? div(div(d_l, st.v, a.off), ln2, a.off) : log_base_bwd(st.v, d_l, sh.lb2, a.off);
         const float d_s2 = APPROX ? mul(recip_n, d_v, a.off) : mul_bwd(st.s2, recip_n, d_v, 0);
 
         // c feeds the division and both operands of pam(c, c)
@@ -279,22 +303,27 @@ int pick_grid(int64_t rows, bool backward) {
 
 template <bool BWD, bool APPROX>
 int launch(const LnArgs& a, int grid, cudaStream_t st) {
-    const bool vec = (a.width & 3) == 0 && aligned16(a.x) && aligned16(a.out) && (!a.w || aligned16(a.w)) &&
-                     (!a.b || aligned16(a.b)) && (!a.dy || aligned16(a.dy));
+    // register layout: VEC consecutive columns per chunk, NCH chunks per lane; the first layout
+    // that holds the row with the fewest register slots wins (192 columns: 3 chunks of 2)
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.out) |
+                           reinterpret_cast<uintptr_t>(a.w) | reinterpret_cast<uintptr_t>(a.b) |
+                           reinterpret_cast<uintptr_t>(a.dy);
+    const bool v4 = (a.width & 3) == 0 && (bits & 15u) == 0;
+    const bool v2 = (a.width & 1) == 0 && (bits & 7u) == 0;
 #define PAMK_LN(V, N)                                                                   \
     do {                                                                                \
         if (BWD) ln_bwd_kernel<V, N, APPROX><<<grid, kThreads, 0, st>>>(a);             \
         else ln_fwd_kernel<V, N><<<grid, kThreads, 0, st>>>(a);                         \
         return check_launch();                                                          \
     } while (0)
-    if (vec) {
-        if (a.width <= 256) PAMK_LN(4, 2);
-        if (a.width <= 512) PAMK_LN(4, 4);
-        if (a.width <= 1024) PAMK_LN(4, 8);
-    } else {
-        if (a.width <= 256) PAMK_LN(1, 8);
-        if (a.width <= 1024) PAMK_LN(1, 32);
-    }
+    if (v4 && a.width <= 128) PAMK_LN(4, 1);
+    if (v2 && a.width <= 192) PAMK_LN(2, 3);
+    if (v4 && a.width <= 256) PAMK_LN(4, 2);
+    if (v4 && a.width <= 512) PAMK_LN(4, 4);
+    if (v4 && a.width <= 768) PAMK_LN(4, 6);
+    if (v4 && a.width <= 1024) PAMK_LN(4, 8);
+    if (a.width <= 256) PAMK_LN(1, 8);
+    if (a.width <= 1024) PAMK_LN(1, 32);
 #undef PAMK_LN
     return PAMK_ERR_SIZE;
 }

@@ -90,6 +90,61 @@ PAM_HD float div_bwd(float a, float b, float dc, int32_t off) {
     return fmul(-fdiv(q, bp), dc);
 }
 
+// ---- division by a divisor that many dividends share ---------------------------------------------
+// pad(a, d) needs the true quotient only to classify it (flush / pass / NaN); the result itself is
+// integer arithmetic.  For a fixed divisor the classification is a pair of thresholds on |a|:
+//     |a| <= flush_max  ->  +0.0f        (exactly the a with  fl(|a| / |d|) <= 0x02081cea)
+//     |a| <= pass_max   ->  bits(a) - bits(d) + (0x3f800000 - off)
+//     otherwise         ->  NaN          (also for NaN a: both comparisons are false)
+// so a row that divides by one value pays one IEEE division per threshold instead of one per
+// element.  make_divisor finds the two largest qualifying magnitudes exactly by correcting the
+// rounded product F * |d| with a few trial divisions.
+struct Divisor {
+    float flush_max, pass_max;   // -1 when no magnitude qualifies
+    int32_t sub;                 // bits(d) - (0x3f800000 - off)
+};
+
+PAM_HD float next_up(float m) { return i2f(f2i(m) + 1); }      // for finite m >= 0
+PAM_HD float next_down(float m) { return i2f(f2i(m) - 1); }    // for finite m > 0
+
+// largest finite m >= 0 with fl(m / d) <= bound, or -1; d > 0 finite, bound > 0 finite
+PAM_HD float largest_dividend(float d, float bound) {
+    const float fmax = i2f(0x7f7fffff);
+    float m = fmul(bound, d);
+    if (!(m <= fmax)) m = fmax;                      // the product overflowed
+    for (int k = 0; k < 4 && fdiv(m, d) > bound; ++k) {
+        if (m == 0.0f) return -1.0f;
+        m = next_down(m);
+    }
+    if (fdiv(m, d) > bound) return -1.0f;            // not reachable for finite d > 0; stay safe
+    for (int k = 0; k < 4 && m < fmax && fdiv(next_up(m), d) <= bound; ++k) m = next_up(m);
+    return m;
+}
+
+PAM_HD Divisor make_divisor(float d, int32_t off) {
+    Divisor r;
+    r.sub = isub(f2i(d), kBias - off);
+    const float ad = fabsf(d);
+    if (ad > 0.0f && ad <= i2f(0x7f7fffff)) {        // finite, non-zero
+        r.flush_max = largest_dividend(ad, i2f(kFlushBits));
+        r.pass_max = largest_dividend(ad, i2f(kPassBits));
+    } else if (ad > 0.0f) {                          // +-inf: finite / inf = 0 flushes, inf / inf = NaN
+        r.flush_max = r.pass_max = i2f(0x7f7fffff);
+        if (ad != ad) r.flush_max = r.pass_max = -1.0f;   // NaN divisor: everything is NaN
+    } else {                                         // zero (a / 0 = inf or NaN) or NaN
+        r.flush_max = r.pass_max = -1.0f;
+    }
+    return r;
+}
+
+// pad(a, d) for the divisor prepared by make_divisor(d, off): same bits as div(a, d, off)
+PAM_HD float div_by(float a, const Divisor& d) {
+    const float mag = fabsf(a);
+    if (mag <= d.flush_max) return 0.0f;
+    if (mag <= d.pass_max) return i2f(isub(f2i(a), d.sub));
+    return quiet_nan();
+}
+
 // 2^e for an integer-valued float e, as an exact double (0 / inf outside double's range)
 PAM_HD double exp2_int_d(float e) {
     if (!(e >= -1100.0f)) return e != e ? (double)e : 0.0;

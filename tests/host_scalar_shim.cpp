@@ -14,3 +14,10 @@ static inline float pa_log2(float x) { return pamk::log2(x); }
 static inline float pa_log2_bwd(float x, float dy) { return pamk::log2_bwd(x, dy); }
 
 #include "../oracle/array_loops.inc"
+
+// pad(a, d) through the shared-divisor form, one divisor per call (for tests/test_scalar_header_host.py)
+extern "C" void host_div_by(const float* a, float d, float* c, int64_t n, int offset) {
+    const pamk::Divisor prepared = pamk::make_divisor(d, offset);
+    #pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) c[i] = pamk::div_by(a[i], prepared);
+}

@@ -68,3 +68,34 @@ def test_exp2_log2_exhaustive_exponents(oracle, host_header):
     t = torch.linspace(-160, 135, 50_000)
     assert_bits_equal(host_header.pa_exp_fwd(t, 2.0, 1.0), K.pa_exp_fwd(t, 2.0, 1.0))
     assert_bits_equal(host_header.pa_exp_bwd(t, t.flip(0), 2.0, 1.0), K.pa_exp_bwd(t, t.flip(0), 2.0, 1.0))
+
+
+def test_shared_divisor_division_is_exact(oracle, host_header):
+    """div_by(a, make_divisor(d)) == pad(a, d) bit for bit: for divisors of every magnitude (and the
+    special ones) against dividends that hug both thresholds of each divisor from either side."""
+    import ctypes
+    K = oracle.kernels()
+    lib = host_header.lib
+    lib.host_div_by.argtypes = [ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
+    lib.host_div_by.restype = None
+    g = torch.Generator().manual_seed(99)
+    raw = torch.randint(-2**31, 2**31 - 1, (20000,), generator=g, dtype=torch.int64).to(torch.int32).view(torch.float32)
+    divisors = [0.0, -0.0, float("inf"), float("-inf"), float("nan"), 1.0, -1.0, 1.4e-45, 1e-40, 1.1754944e-38,
+                3.4028235e38, 1e37, 9.9e36, 1e-37, 1.0000001e-37, 0.33333334, 3.0, 192.0, 1e-19, 1e19]
+    divisors += (torch.randn(60, generator=g) * torch.exp2(torch.randint(-126, 127, (60,), generator=g).float())).tolist()
+    steps = torch.arange(-6, 7, dtype=torch.int32)
+    for d in divisors:
+        dt = torch.tensor(d, dtype=torch.float32)
+        for offset in (1.0, 1.0552):
+            cands = [raw, torch.tensor([0.0, -0.0, float("inf"), float("-inf"), float("nan")])]
+            if bool(dt.isfinite()) and float(dt) != 0.0:
+                for bound_bits in (0x02081CEA, 0x7CF0BDC2):
+                    centre = (torch.tensor(bound_bits, dtype=torch.int32).view(torch.float32) * dt.abs()).reshape(1)
+                    if bool(centre.isfinite()):
+                        around = (centre.view(torch.int32) + steps).clamp(0, 0x7F7FFFFF).view(torch.float32)
+                        cands += [around, -around]
+            a = torch.cat(cands).contiguous()
+            got = torch.empty_like(a)
+            lib.host_div_by(a.data_ptr(), float(dt), got.data_ptr(), a.numel(), oracle.offset_to_int(offset))
+            want = K.pad_fwd(a, dt.expand_as(a).contiguous(), offset)
+            assert_bits_equal(got, want, f"divisor {d!r} offset {offset}")
