@@ -293,11 +293,11 @@ __global__ void __launch_bounds__(kGradWarps * 32) ln_param_grad_kernel(const fl
     }
 }
 
-// Forward: enough CTAs for 64 resident warps per SM.  Backward: fewer, longer-lived CTAs (each warp
-// walks several rows), which keeps the per-CTA partial sums for dweight / dbias few.
+// Enough CTAs to fill the resident-warp slots of every SM (the backward kernel needs more registers,
+// so fewer of its CTAs fit); warps walk the rows with a grid stride.
 int pick_grid(int64_t rows, bool backward) {
     const int64_t want = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
-    const int64_t cap = (int64_t)sm_count() * (backward ? 4 : 16);
+    const int64_t cap = (int64_t)sm_count() * (backward ? 12 : 16);
     return (int)(want < cap ? want : cap);
 }
 

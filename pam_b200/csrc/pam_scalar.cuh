@@ -59,10 +59,9 @@ PAM_HD int32_t offset_bits(float offset) { return isub(f2i(offset), kBias); }
 // product/quotient; tiny -> +0.0f (sign dropped), in range -> the integer-arithmetic result,
 // otherwise (overflow, inf, NaN) -> NaN.
 PAM_HD float range_rule(float t, int32_t candidate) {
-    const float mag = fabsf(t);
-    if (mag <= i2f(kFlushBits)) return 0.0f;
-    if (mag <= i2f(kPassBits)) return i2f(candidate);
-    return quiet_nan();
+    const float mag = fabsf(t);                       // two compares and two selects, no branch
+    const float kept = mag <= i2f(kPassBits) ? i2f(candidate) : quiet_nan();
+    return mag <= i2f(kFlushBits) ? 0.0f : kept;
 }
 
 // cuda_kernels.cu:15-38
@@ -104,21 +103,23 @@ struct Divisor {
     int32_t sub;                 // bits(d) - (0x3f800000 - off)
 };
 
-PAM_HD float next_up(float m) { return i2f(f2i(m) + 1); }      // for finite m >= 0
-PAM_HD float next_down(float m) { return i2f(f2i(m) - 1); }    // for finite m > 0
-
-// largest finite m >= 0 with fl(m / d) <= bound, or -1; d > 0 finite, bound > 0 finite
+// Largest finite m >= 0 with fl(m / d) <= bound, for finite d > 0 and a finite bound > 0 whose
+// last mantissa bit is 0 (true of both thresholds).  Under round-to-nearest-even fl(q) <= bound
+// holds exactly for q <= mid, the midpoint between bound and the next float (a tie goes to the
+// even neighbour, which is bound).  So m qualifies iff m <= d * mid; that product is exact in
+// double (24 x 25 significant bits) and is rounded toward zero to fp32.
 PAM_HD float largest_dividend(float d, float bound) {
+    const double mid = 0.5 * ((double)bound + (double)i2f(f2i(bound) + 1));
+    const double limit = (double)d * mid;
+#if defined(__CUDA_ARCH__)
+    return __double2float_rz(limit);
+#else
     const float fmax = i2f(0x7f7fffff);
-    float m = fmul(bound, d);
-    if (!(m <= fmax)) m = fmax;                      // the product overflowed
-    for (int k = 0; k < 4 && fdiv(m, d) > bound; ++k) {
-        if (m == 0.0f) return -1.0f;
-        m = next_down(m);
-    }
-    if (fdiv(m, d) > bound) return -1.0f;            // not reachable for finite d > 0; stay safe
-    for (int k = 0; k < 4 && m < fmax && fdiv(next_up(m), d) <= bound; ++k) m = next_up(m);
+    if (limit >= (double)fmax) return fmax;
+    float m = (float)limit;                          // round to nearest, then step down if it went up
+    if ((double)m > limit) m = i2f(f2i(m) - 1);
     return m;
+#endif
 }
 
 PAM_HD Divisor make_divisor(float d, int32_t off) {
@@ -130,8 +131,7 @@ PAM_HD Divisor make_divisor(float d, int32_t off) {
         r.pass_max = largest_dividend(ad, i2f(kPassBits));
     } else if (ad > 0.0f) {                          // +-inf: finite / inf = 0 flushes, inf / inf = NaN
         r.flush_max = r.pass_max = i2f(0x7f7fffff);
-        if (ad != ad) r.flush_max = r.pass_max = -1.0f;   // NaN divisor: everything is NaN
-    } else {                                         // zero (a / 0 = inf or NaN) or NaN
+    } else {                                         // zero (a / 0 = inf or NaN) or NaN: all NaN
         r.flush_max = r.pass_max = -1.0f;
     }
     return r;
@@ -140,9 +140,8 @@ PAM_HD Divisor make_divisor(float d, int32_t off) {
 // pad(a, d) for the divisor prepared by make_divisor(d, off): same bits as div(a, d, off)
 PAM_HD float div_by(float a, const Divisor& d) {
     const float mag = fabsf(a);
-    if (mag <= d.flush_max) return 0.0f;
-    if (mag <= d.pass_max) return i2f(isub(f2i(a), d.sub));
-    return quiet_nan();
+    const float kept = mag <= d.pass_max ? i2f(isub(f2i(a), d.sub)) : quiet_nan();
+    return mag <= d.flush_max ? 0.0f : kept;
 }
 
 // 2^e for an integer-valued float e, as an exact double (0 / inf outside double's range)

@@ -157,8 +157,9 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
         const float total = group_sum<WARPS>(part, scratch);
 
         if (OP == kSoftmaxFwd) {
+            const Divisor by_total = make_divisor(total, off);
 #pragma unroll
-            for (int i = 0; i < NCH * VEC; ++i) e.v[i] = div(e.v[i], total, off);
+            for (int i = 0; i < NCH * VEC; ++i) e.v[i] = div_by(e.v[i], by_total);
             e.store(a.out + row * a.len, a.len, t);
         } else if (OP == kLseFwd) {
             // log2 of the row sum runs with offset 0 whatever the call's offset (pam_ops.py:341)
@@ -167,11 +168,12 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
         } else if (OP == kSoftmaxBwd) {
             R g;
             g.load(a.g + row * a.len, a.len, t, 0.0f);
-            const float recip = div(1.0f, total, off);
+            const Divisor by_total = make_divisor(total, off);
+            const float recip = div_by(1.0f, by_total);
             float dsum = 0.0f;
 #pragma unroll
             for (int i = 0; i < NCH * VEC; ++i) {
-                const float dden = APPROX ? -mul(div(div(e.v[i], total, off), total, off), g.v[i], off)
+                const float dden = APPROX ? -mul(div_by(div_by(e.v[i], by_total), by_total), g.v[i], off)
                                           : div_bwd(e.v[i], total, g.v[i], off);
                 if (R::col(i, t) < a.len) dsum = fadd(dsum, dden);
                 g.v[i] = APPROX ? mul(recip, g.v[i], off) : mul_bwd(e.v[i], recip, g.v[i], 0);

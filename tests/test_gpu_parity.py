@@ -421,7 +421,7 @@ def _ln_case(pam, dev, rows, width, affine, approx, offset, seed):
     y.backward(gy.to(dev))
     vec = _ln_vec(width)
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    grid = min((rows + 3) // 4, sms * 4)                     # CTAs of the backward kernel
+    grid = min((rows + 3) // 4, sms * 12)                    # CTAs of the backward kernel
     chain = E.Chain(offset, E.kernel_rowsum(vec), E.kernel_colsum(rows, grid))
     want = chain.run(x, w, b, gy, 1e-5, approx)
     got = (y, xd.grad, wd.grad if affine else None, bd.grad if affine else None)
@@ -434,7 +434,7 @@ def test_fused_layer_norm_bit_exact_against_replayed_chain(pam, dev, width, appr
     """The kernel against the CPU replay of its own chain in its own summation order: every output
     and gradient bit for bit.  (The same chain summed with torch.sum is checked against the
     reference's fixtures in test_oracle_golden.py.)"""
-    for affine, offset, rows in ((True, None, 37), (False, 1.0552, 5), (True, None, 2500)):
+    for affine, offset, rows in ((True, None, 37), (False, 1.0552, 5), (True, None, 7500)):
         if rows > 100 and width not in (48, 192):
             continue                                          # the long case walks several rows per warp
         got, want = _ln_case(pam, dev, rows, width, affine, approx, offset, width)
