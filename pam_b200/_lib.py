@@ -112,6 +112,13 @@ def stream_ptr(device):
     return torch.cuda.current_stream(device).cuda_stream
 
 
+import contextlib
+
+_NO_GUARD = contextlib.nullcontext()
+
+
 def device_guard(device):
-    """Makes `device` current for the duration of a kernel launch."""
+    """Makes `device` current for the duration of a kernel launch (free when it already is)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_GUARD
     return torch.cuda.device(device)

@@ -54,36 +54,51 @@ __device__ __forceinline__ float splat_value(const Operand& o) {
 
 struct PamFwd {
     int32_t off;
+    __device__ void prepare() {}
     __device__ float operator()(float a, float b, float) const { return mul(a, b, off); }
 };
 struct PadFwd {
     int32_t off;
+    __device__ void prepare() {}
     __device__ float operator()(float a, float b, float) const { return div(a, b, off); }
 };
 struct PamBwd {
     int32_t off;
+    __device__ void prepare() {}
     __device__ float operator()(float a, float b, float dc) const { return mul_bwd(a, b, dc, off); }
 };
 struct PadBwd {
     int32_t off;
+    __device__ void prepare() {}
     __device__ float operator()(float a, float b, float dc) const { return div_bwd(a, b, dc, off); }
 };
 // Unary ops take x in slot 0 and, for the backward forms, dy in slot 1.
 struct ExpFwd {
     int32_t off; float base;
+    __device__ void prepare() {}
     __device__ float operator()(float x, float, float) const { return exp_base(x, log2f(base), off); }
 };
 struct ExpBwd {
     int32_t off; float base;
+    __device__ void prepare() {}
     __device__ float operator()(float x, float dy, float) const { return exp_base_bwd(x, dy, log2f(base), off); }
 };
+// log_base(x) = pad(log2 x, log2f(base)): the divisor is the same for every element, so its two
+// range thresholds are prepared once per thread (pam_scalar.cuh make_divisor) instead of dividing
+// per element.  prepare() runs once per thread before the first element.
 struct LogFwd {
     int32_t off; float base;
-    __device__ float operator()(float x, float, float) const { return log_base(x, log2f(base), off); }
+    Divisor by_lb;
+    __device__ void prepare() { by_lb = make_divisor(log2f(base), off); }
+    __device__ float operator()(float x, float, float) const { return div_by(log2(x), by_lb); }
 };
 struct LogBwd {
     int32_t off; float base;
-    __device__ float operator()(float x, float dy, float) const { return log_base_bwd(x, dy, log2f(base), off); }
+    float inv_lb;                                   // pad(1, log2f(base))
+    __device__ void prepare() { inv_lb = div(1.0f, log2f(base), off); }
+    __device__ float operator()(float x, float dy, float) const {
+        return log2_bwd(x, mul_bwd(log2(x), inv_lb, dy, 0));
+    }
 };
 
 constexpr int kThreads = 256;
@@ -97,6 +112,7 @@ constexpr int kPerBlock = kThreads * kPerThread;
 template <class Op, int NIN, bool VEC>
 __global__ void __launch_bounds__(kThreads, NIN > 2 ? 6 : 8) ew_kernel(Op op, Operand o0, Operand o1, Operand o2,
                                                          float* __restrict__ out, Shape s) {
+    op.prepare();
     const float s0 = splat_value(o0);
     const float s1 = NIN > 1 ? splat_value(o1) : 0.0f;
     const float s2 = NIN > 2 ? splat_value(o2) : 0.0f;

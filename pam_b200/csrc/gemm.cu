@@ -293,7 +293,7 @@ gemm_kernel(const GemmParams p) {
                     for (int j = 0; j < 8; ++j) acc[i][j] = fadd(acc[i][j], i2f(PAMK_PRODUCT(a[i], b[j])));
             }
         } else if (MODE == kPam && path == kFlush) {
-#pragma unroll 2
+#pragma unroll 4
             for (int kk = 0; kk < BK; ++kk) {
                 PAMK_FRAGMENTS(kk)
                 float araw[8];          // a[] holds pre-biased patterns; the product needs the values
