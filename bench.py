@@ -41,7 +41,8 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--case", default=None,
                     help="run one kernel in isolation (for profiling) instead of the benchmark: "
-                         "gemm | gemm_specials | deit_gemms | mul | layer_norm_fwd | layer_norm_bwd")
+                         "gemm | gemm_specials | deit_gemms | mul | layer_norm_fwd | layer_norm_bwd | "
+                         "softmax_fwd | softmax_bwd | adam")
     ap.add_argument("--size", type=int, default=4096, help="--case size: GEMM edge, or log2 of the element count")
     ap.add_argument("--reps", type=int, default=2)
     return ap.parse_args()
@@ -357,6 +358,28 @@ def run_case(args):
             fn = lambda: torch.autograd.grad(y, (x, ln.weight, ln.bias), gy, retain_graph=True)
             work = 12.0 * rows * LN_WIDTH
         unit = "B"
+    elif args.case in ("softmax_fwd", "softmax_bwd"):
+        length = 1024
+        rows = (1 << n if n < 40 else n) // length
+        x = torch.randn(rows, length, device=dev, requires_grad=True)
+        gy = torch.randn(rows, length, device=dev)
+        if args.case == "softmax_fwd":
+            def fn():
+                with torch.no_grad():
+                    pam.softmax(x, dim=-1, approx_bwd=True)
+            work = 12.0 * rows * length           # maximum pass 4 B + row pass 8 B per element
+        else:
+            y = pam.softmax(x, dim=-1, approx_bwd=True)
+            fn = lambda: torch.autograd.grad(y, (x,), gy, retain_graph=True)
+            work = 16.0 * rows * length           # maximum pass 4 B + row pass 12 B per element
+        unit = "B"
+    elif args.case == "adam":
+        from pam_b200 import optim
+        count = 1 << n if n < 40 else n
+        p = torch.nn.Parameter(torch.randn(count, device=dev))
+        p.grad = torch.randn(count, device=dev) * 0.01
+        opt = optim.Adam([p], lr=5e-4, betas=(0.9, 0.98), weight_decay=1e-4, opt_functional_cfg="pam")
+        fn, work, unit = opt.step, 28.0 * count, "B"
     else:
         raise SystemExit(f"unknown --case {args.case}")
     fn()

@@ -80,3 +80,35 @@ def test_deit_block_forward_backward_and_adam_step(oracle):
         want, _, _ = oracle.adam_step(params[k], cpu[k].grad, torch.zeros_like(params[k]), torch.zeros_like(params[k]),
                                       step=1, lr=5e-4, betas=(0.9, 0.98), eps=1e-8, weight_decay=0.05)
         assert torch.equal(gpu[k].detach().cpu().view(torch.int32), want.view(torch.int32)), f"adam {k}"
+
+
+def test_vocabulary_loss_path(oracle):
+    """The loss head of the 6+6-layer translation model of BASELINE config 3: tied output projection
+    as a PAM GEMM onto a 10000-word vocabulary, PAM log-softmax over the vocabulary (rows of 10000:
+    the CTA-per-row kernel), label-smoothed NLL with PAM scaling (fairseq criterions/
+    label_smoothed_cross_entropy.py:36-54 through the operator dictionary), forward and backward."""
+    import pam_b200 as pam
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(31)
+    tokens, d_model, vocab, eps_ls = 96, 512, 10000, 0.1
+    feats = torch.randn(tokens, d_model, generator=g)
+    emb = torch.randn(vocab, d_model, generator=g) * d_model ** -0.5
+    target = torch.randint(4, vocab, (tokens,), generator=g)
+
+    def loss_fn(ops, feats, emb, target):
+        logits = ops.linear(feats, emb, **KW)
+        lprobs = ops.log_softmax(logits, dim=-1, **KW)
+        nll = -lprobs.gather(-1, target.unsqueeze(-1)).sum()
+        smooth = -lprobs.sum()
+        eps_i = ops.div(eps_ls, vocab - 1)
+        return ops.mul(nll, 1.0 - eps_ls - eps_i, **KW) + ops.mul(smooth, eps_i, **KW)
+
+    fc, ec = feats.clone().requires_grad_(), emb.clone().requires_grad_()
+    lc = loss_fn(oracle, fc, ec, target)
+    lc.backward()
+    fg, eg = feats.to(dev).requires_grad_(), emb.to(dev).requires_grad_()
+    lg = loss_fn(pam, fg, eg, target.to(dev))
+    lg.backward()
+    assert_close_nan(lg.reshape(1), lc.reshape(1), 1e-4, 1e-4, "loss")
+    assert_close_nan(fg.grad, fc.grad, 5e-3, 5e-3 * float(fc.grad.abs().max()), "d features")
+    assert_close_nan(eg.grad, ec.grad, 5e-3, 5e-3 * float(ec.grad.abs().max()), "d embedding")
