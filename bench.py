@@ -68,7 +68,7 @@ def make_inputs(seed, device=None, pin=False):
 # ---- clocks ---------------------------------------------------------------------------------------
 
 class ClockSampler:
-    """Samples nvidia-smi for one GPU every 200 ms while the timed region runs."""
+    """Samples nvidia-smi for one GPU every 20 ms while the device-timed regions run."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
@@ -80,7 +80,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -169,14 +169,15 @@ def run_ours(args):
     # ---- value: inputs resident in HBM, per-step CUDA events, L2 flushed between steps ----------
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     launches0 = lib.pamk_launch_count()
-    with ClockSampler(local) as clocks:
-        barrier()
-        for e0, e1 in ev:
-            flush.zero_()
-            e0.record()
-            step(d)
-            e1.record()
-        barrier()
+    clocks = ClockSampler(local)
+    clocks.__enter__()
+    barrier()
+    for e0, e1 in ev:
+        flush.zero_()
+        e0.record()
+        step(d)
+        e1.record()
+    barrier()
     launches = lib.pamk_launch_count() - launches0
     total_ms = sum(e0.elapsed_time(e1) for e0, e1 in ev)
 
@@ -211,6 +212,7 @@ def run_ours(args):
                                        torch.cuda.current_stream().cuda_stream), "issue_rate")
         peak[name] = steps_done.value / (ms.value * 1e-3)
     mac_peak = max(peak["iadd_fadd"], peak["imad_fadd"], peak["mixed_fadd"])
+    clocks.__exit__(None, None, None)
 
     # ---- e2e: host buffers in, results out, through the public API ------------------------------------
     # Copies are pipelined against the compute per layer on two extra streams (PCIe is full duplex):

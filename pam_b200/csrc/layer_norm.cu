@@ -142,34 +142,44 @@ __device__ __forceinline__ void centre_and_stats(RowRegs<VEC, NCH>& c, RowStats&
     finish_stats(st, a, sh);
 }
 
+// Minimum resident CTAs asked of the compiler: narrow layouts need few registers, and the more warps
+// an SM holds the more loads it has in flight.
+constexpr int min_ctas(int slots, bool backward) {
+    return slots <= 8 ? (backward ? 6 : 10) : (slots <= 16 ? (backward ? 4 : 6) : 1);
+}
+
 template <int VEC, int NCH>
-__global__ void __launch_bounds__(kThreads) ln_fwd_kernel(const LnArgs a) {
+__global__ void __launch_bounds__(kThreads, min_ctas(VEC * NCH, false)) ln_fwd_kernel(const LnArgs a) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
     const Shared sh = make_shared(a.nf, a.off);
-    RowRegs<VEC, NCH> w, b;
-    if (a.w) load_row<VEC, NCH>(w, a.w, a.width, lane, 1.0f);
-    if (a.b) load_row<VEC, NCH>(b, a.b, a.width, lane, 0.0f);
     for (int64_t row = warp; row < a.rows; row += nwarps) {
         RowRegs<VEC, NCH> c;
         load_row<VEC, NCH>(c, a.x + row * a.width, a.width, lane, 0.0f);
         RowStats st;
         centre_and_stats<VEC, NCH>(c, st, a, sh, lane);
         const Divisor by_denom = make_divisor(st.denom, a.off);
+        // weight and bias are re-read per row (they stay in L1) rather than held in registers for
+        // the whole kernel: the registers buy more resident warps
+        RowRegs<VEC, NCH> p;
+        if (a.w) load_row<VEC, NCH>(p, a.w, a.width, lane, 1.0f);
 #pragma unroll
         for (int i = 0; i < NCH * VEC; ++i) {
-            float y = div_by(c.v[i], by_denom);
-            if (a.w) y = mul(y, w.v[i], a.off);
-            if (a.b) y = fadd(y, b.v[i]);
-            c.v[i] = y;
+            const float y = div_by(c.v[i], by_denom);
+            c.v[i] = a.w ? mul(y, p.v[i], a.off) : y;
+        }
+        if (a.b) {
+            load_row<VEC, NCH>(p, a.b, a.width, lane, 0.0f);
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) c.v[i] = fadd(c.v[i], p.v[i]);
         }
         store_row<VEC, NCH>(c, a.out + row * a.width, a.width, lane);
     }
 }
 
 template <int VEC, int NCH, bool APPROX>
-__global__ void __launch_bounds__(kThreads) ln_bwd_kernel(const LnArgs a) {
+__global__ void __launch_bounds__(kThreads, min_ctas(VEC * NCH, true)) ln_bwd_kernel(const LnArgs a) {
     __shared__ float stage[kWarpsPerCta][NCH * VEC][32];
     const int lane = threadIdx.x & 31;
     const int wid = threadIdx.x >> 5;
