@@ -271,9 +271,9 @@ __global__ void __launch_bounds__(kThreads, min_ctas(VEC * NCH, true)) ln_bwd_ke
 }
 
 // dw[c] = sum over CTAs of partials[cta][0][c], db likewise.  One CTA per 32 columns; warp j adds
-// the partials of CTAs j, j + 8, j + 16, ... in that order, then the eight warp sums are added in
+// the partials of CTAs j, j + 32, j + 64, ... in that order, then the 32 warp sums are added in
 // warp order.
-constexpr int kGradWarps = 8;
+constexpr int kGradWarps = 32;
 __global__ void __launch_bounds__(kGradWarps * 32) ln_param_grad_kernel(const float* __restrict__ partials,
                                                                        float* __restrict__ dw, float* __restrict__ db,
                                                                        int ctas, int width) {
@@ -282,6 +282,7 @@ __global__ void __launch_bounds__(kGradWarps * 32) ln_param_grad_kernel(const fl
     const int col = blockIdx.x * 32 + lane;
     float sw = 0.0f, sb = 0.0f;
     if (col < width) {
+#pragma unroll 4
         for (int k = wid; k < ctas; k += kGradWarps) {
             sw = fadd(sw, __ldg(partials + ((int64_t)k * 2) * width + col));
             sb = fadd(sb, __ldg(partials + ((int64_t)k * 2 + 1) * width + col));

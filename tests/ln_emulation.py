@@ -160,10 +160,10 @@ def kernel_rowsum(vec, warps=1):
     return rowsum
 
 
-def kernel_colsum(rows_total, grid, warps_per_cta=4, grad_warps=8):
+def kernel_colsum(rows_total, grid, warps_per_cta=4, grad_warps=32):
     """Order of the dweight / dbias sums in the kernel: warp w of CTA c adds its rows
     (c*4 + w, + grid*4, ...) in order from +0; the four warps of a CTA are added in order; the
-    second kernel's warp j adds the CTA sums j, j + 8, ... in order from +0 and the eight warp
+    second kernel's warp j adds the CTA sums j, j + 32, ... in order from +0 and the 32 warp
     sums are added in order."""
     def colsum(t):
         rows, n = t.shape
