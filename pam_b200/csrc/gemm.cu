@@ -33,6 +33,11 @@
 #ifndef PAMK_IADD3
 #define PAMK_IADD3 0
 #endif
+// Timing experiment only (never set in shipped builds): skip the exponent-range bookkeeping and run
+// the two-instruction loop unconditionally, to measure what the bookkeeping costs.
+#ifndef PAMK_EXPERIMENT_NOSTATS
+#define PAMK_EXPERIMENT_NOSTATS 0
+#endif
 
 namespace pamk {
 namespace {
@@ -233,7 +238,7 @@ gemm_kernel(const GemmParams p) {
         load_slab<T, BN, T::kTasksB, B_KC, VEC>(rb, p.B, Bb, n0, p.N, k0, k_end, tid);
     };
     auto stage_store = [&](int buf, int slot) {
-        if (MODE == kPam) {
+        if (MODE == kPam && !PAMK_EXPERIMENT_NOSTATS) {
             int lo_a, hi_a, lo_b, hi_b;
             minmax_bits(ra, lo_a, hi_a);
             minmax_bits(rb, lo_b, hi_b);
@@ -266,7 +271,7 @@ gemm_kernel(const GemmParams p) {
         const bool more = s + 1 < slabs;
         if (more) stage_load(k_begin + (s + 1) * BK);
         int path = kFast;
-        if (MODE == kPam) {
+        if (MODE == kPam && !PAMK_EXPERIMENT_NOSTATS) {
             const int slot = s % 3;
             path = classify(stats[slot][0], stats[slot][1], stats[slot][2], stats[slot][3]);
             // the slot two slabs ahead was last read before the previous barrier: reset it now
