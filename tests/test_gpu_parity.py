@@ -396,6 +396,93 @@ def test_square_gemm_4096_with_specials_sampled(pam, K, dev):
     assert bool(bits_equal(Cp, C[perm]).all())
 
 
+# ---- the reference's own test recipes, run as the reference runs them ---------------------------------
+
+def test_reference_recipe_conv_and_bmm_power_of_two_equivalence(pam, dev):
+    """pam/test_pam.py:151-216: with power-of-two weights and short-mantissa inputs PAM equals true
+    multiplication, so conv2d / grouped conv / bmm must match torch's outputs and both gradients
+    (odd sizes exercise the tile edges)."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    g = torch.Generator().manual_seed(17)
+    close = lambda a, b: torch.allclose(a, b, rtol=1e-5, atol=1e-3)
+
+    X = (torch.randint(-1024, 1024, (11, 13, 15, 17), generator=g) / 64.0).to(dev).requires_grad_()
+    W = (2.0 ** torch.randint(-8, 8, (19, 13, 3, 5), generator=g)).to(dev).requires_grad_()
+    X2, W2 = X.detach().clone().requires_grad_(), W.detach().clone().requires_grad_()
+    Y = pam.conv2d(X, W, approx_bwd=True)
+    Y.sum().backward()
+    Y2 = torch.nn.functional.conv2d(X2, W2)
+    Y2.sum().backward()
+    assert close(Y, Y2) and close(X.grad, X2.grad) and close(W.grad, W2.grad)
+
+    for G in (1, 8):
+        X = (torch.randint(-8, 9, (11, 16, 15, 17), generator=g) / 4.0).to(dev).requires_grad_()
+        W = (2.0 ** torch.randint(-2, 3, (128, 16 // G, 3, 5), generator=g)).to(dev).requires_grad_()
+        X2, W2 = X.detach().clone().requires_grad_(), W.detach().clone().requires_grad_()
+        Y = pam.conv2d_group(X, W, groups=G, approx_bwd=True)
+        Y.sum().backward()
+        Y2 = torch.nn.functional.conv2d(X2, W2, groups=G)
+        Y2.sum().backward()
+        assert close(Y, Y2) and close(X.grad, X2.grad) and close(W.grad, W2.grad)
+
+    X = (torch.randint(-128, 128, (11, 13, 15), generator=g) / 64.0).to(dev).requires_grad_()
+    W = (2.0 ** torch.randint(-8, 8, (11, 15, 19), generator=g)).to(dev).requires_grad_()
+    X2, W2 = X.detach().clone().requires_grad_(), W.detach().clone().requires_grad_()
+    Y = pam.bmm(X, W, approx_bwd=True)
+    Y.sum().backward()
+    Y2 = torch.bmm(X2, W2)
+    Y2.sum().backward()
+    assert close(Y, Y2) and close(X.grad, X2.grad) and close(W.grad, W2.grad)
+
+
+def test_reference_recipe_exact_gradient_and_bmm_bwd(pam, oracle, dev):
+    """pam/test_pam.py:48-73 (exact backward of the elementwise product on exponents in [-30, 30))
+    and :219-239 (batched product with the exact backward), against the oracle."""
+    g = torch.Generator().manual_seed(18)
+    n = 128
+    A = (2.0 ** torch.randint(-30, 30, (n,), generator=g)) * (1 + torch.rand(n, generator=g))
+    B = (2.0 ** torch.randint(-30, 30, (n,), generator=g)) * (1 + torch.rand(n, generator=g))
+    dC = torch.arange(n).float()
+    A1, B1 = A.to(dev).requires_grad_(), B.to(dev).requires_grad_()
+    pam.cuda_bindings.pam(A1, B1).backward(dC.to(dev))
+    A2, B2 = A.clone().requires_grad_(), B.clone().requires_grad_()
+    oracle.mul(A2, B2).backward(dC)
+    assert_bits_equal(A1.grad, A2.grad)
+    assert_bits_equal(B1.grad, B2.grad)
+
+    X = torch.randint(-1024, 1024, (11, 13, 15), generator=g) / 32.0
+    W = torch.randint(-1024, 1024, (11, 15, 19), generator=g) / 32.0
+    X1, W1 = X.to(dev).requires_grad_(), W.to(dev).requires_grad_()
+    Y1 = pam.bmm(X1, W1, approx_bwd=False)
+    Y1.sum().backward()
+    X2, W2 = X.clone().requires_grad_(), W.clone().requires_grad_()
+    Y2 = oracle.bmm(X2, W2, approx_bwd=False)
+    Y2.sum().backward()
+    assert_bits_equal(Y1, Y2)
+    assert_bits_equal(X1.grad, X2.grad)
+    assert_bits_equal(W1.grad, W2.grad)
+
+
+def test_empty_and_degenerate_inputs(pam, dev):
+    e = torch.empty(0, device=dev)
+    assert pam.mul(e, e).shape == (0,) and pam.div(e, 2.0).shape == (0,) and pam.exp2(e).shape == (0,)
+    assert pam.matmul(torch.empty(0, 5, device=dev), torch.ones(5, 3, device=dev)).shape == (0, 3)
+    z = pam.matmul(torch.ones(4, 0, device=dev), torch.ones(0, 3, device=dev))          # K = 0: all sums are +0
+    assert z.shape == (4, 3) and bool((z == 0).all())
+    assert pam.bmm(torch.empty(0, 2, 3, device=dev), torch.empty(0, 3, 4, device=dev)).shape == (0, 2, 4)
+    ln = pam.LayerNorm(8).to(dev)
+    assert ln(torch.empty(0, 8, device=dev)).shape == (0, 8)
+    assert pam.softmax(torch.empty(0, 7, device=dev), dim=-1).shape == (0, 7)
+    one = pam.softmax(torch.tensor([[3.0]], device=dev), dim=-1)                          # single-entry rows
+    assert one.item() == 1.0
+    # non-contiguous inputs: a strided view and a transposed matrix give the contiguous copy's result
+    x = torch.randn(16, 32, device=dev)
+    assert torch.equal(pam.mul(x[:, ::2], 1.5), pam.mul(x[:, ::2].contiguous(), 1.5))
+    assert torch.equal(pam.softmax(x.T, dim=-1), pam.softmax(x.T.contiguous(), dim=-1))
+    assert torch.equal(pam.layer_norm(x.T, (16,)), pam.layer_norm(x.T.contiguous(), (16,)))
+
+
 # ---- fused layer normalisation ---------------------------------------------------------------------
 
 def _ln_vec(width):
