@@ -15,11 +15,11 @@
 //     the A side is pre-biased (bits - (0x3f800000 - offset)) so that the product is a single
 //     add, both sides are laid out [k][row] whatever their layout in global memory (the four
 //     row-/column-major combinations of the reference become two loader variants per side), and
-//     the exponent range of the slab is recorded;
+//     every element's exponent is tested against the safe band;
 //   * the reference's per-product range rule (flush below 1e-37, NaN above 1e37 or for
-//     inf/NaN; epfml/pam pam/cuda_kernels.cu:24-37) is hoisted: when the recorded exponent ranges
-//     prove that every product of the slab is in range, the slab runs the two-instruction loop;
-//     otherwise it runs a loop that evaluates the true fp32 product and applies the rule
+//     inf/NaN; epfml/pam pam/cuda_kernels.cu:24-37) is hoisted: when every element of the slab has
+//     its exponent in a band that keeps all products in range, the slab runs the two-instruction
+//     loop; otherwise it runs a loop that evaluates the true fp32 product and applies the rule
 //     exactly.  Either way every product equals the reference's bit for bit;
 //   * each output is summed by one thread, strictly in k order, from +0.0f — the same order as
 //     the reference's kernel (cuda_kernels.cu:608-629), so without split-K the sums are
@@ -147,32 +147,41 @@ __device__ __forceinline__ void store_slab(float* s, const float (&r)[NT * 4], i
     }
 }
 
-template <int N>
-__device__ __forceinline__ void minmax_bits(const float (&r)[N], int& lo, int& hi) {
-    lo = 0x7fffffff;
-    hi = 0;
-#pragma unroll
-    for (int c = 0; c < N; ++c) {
-        const int m = f2i(r[c]) & 0x7fffffff;
-        lo = min(lo, m);
-        hi = max(hi, m);
-    }
-}
-
-// Which loop a slab may run, from the biased-exponent ranges of its two operands.
-//   products of normal finite numbers satisfy 2^(ea+eb-254) <= |a*b| <= 2^(ea+eb-252), so
-//   ea+eb >= 132 puts every product above 1e-37 and ea+eb <= 374 keeps it below 1e37.
-//   kFast:    every product in range: add the bit patterns, accumulate.
-//   kFlush:   no product can reach 1e37 and no operand is inf/NaN, but some may be tiny or zero:
-//             evaluate the true product and skip the ones that flush.
-//   kFull:    anything goes: the complete three-way rule.
+// ---- which loop a slab may run ---------------------------------------------------------------------
+// Products of normal finite numbers satisfy 2^(ea+eb-254) <= |a*b| <= 2^(ea+eb-252) (ea, eb the
+// biased exponents), so if every element of both operand slabs has its exponent field in the band
+// [66, 187] every product lies in [2^-122, 2^122], inside the reference's pass range (1e-37, 1e37):
+//   kFast:  all elements in the band: add the bit patterns, accumulate.
+//   kFlush: some element below the band (zero, denormal, tiny) but none above it: no product can
+//           reach 1e37 and no operand is inf / NaN; evaluate the true product, skip what flushes.
+//   kFull:  some element above the band: the complete three-way rule.
+// The band test is one three-input add and one unsigned max per element: 2 * bits drops the sign,
+// minus twice the band's lower bound makes "below" wrap around to huge values.
 enum Path { kFast = 0, kFlush = 1, kFull = 2 };
 
-__device__ __forceinline__ int classify(int minA, int maxA, int minB, int maxB) {
-    const int ea0 = minA >> 23, ea1 = maxA >> 23, eb0 = minB >> 23, eb1 = maxB >> 23;
-    const bool bounded = ea1 <= 254 && eb1 <= 254 && ea1 + eb1 <= 374;
-    const bool large = ea0 >= 1 && eb0 >= 1 && ea0 + eb0 >= 132;
-    return bounded ? (large ? kFast : kFlush) : kFull;
+constexpr uint32_t kBandLo2 = 2u * (66u << 23);                // 2 * smallest in-band magnitude
+constexpr uint32_t kBandSpan2 = 2u * ((188u - 66u) << 23);     // in band iff 2*bits - kBandLo2 < span
+constexpr uint32_t kBandHi2 = 2u * (188u << 23);               // 2 * smallest magnitude above the band
+
+template <int N>
+__device__ __forceinline__ uint32_t band_excess(const float (&r)[N], uint32_t vmax) {
+#pragma unroll
+    for (int c = 0; c < N; ++c) {
+        const uint32_t b = (uint32_t)f2i(r[c]);
+        vmax = max(vmax, b + b - kBandLo2);
+    }
+    return vmax;
+}
+
+template <int N>
+__device__ __forceinline__ unsigned above_band(const float (&r)[N]) {
+    unsigned any = 0;
+#pragma unroll
+    for (int c = 0; c < N; ++c) {
+        const uint32_t b = (uint32_t)f2i(r[c]);
+        any |= (b + b >= kBandHi2) ? 2u : 0u;
+    }
+    return any;
 }
 
 template <int MODE, class T, bool A_KC, bool B_KC, bool VEC>
@@ -181,7 +190,7 @@ gemm_kernel(const GemmParams p) {
     constexpr int BM = T::BM, BN = T::BN, BK = T::BK;
     __shared__ __align__(16) float As[2][BK * BM];
     __shared__ __align__(16) float Bs[2][BK * BN];
-    __shared__ int stats[3][4];   // per slab: min/max magnitude bits of A and of B
+    __shared__ unsigned flags[3];   // per slab: bit 0 = an element outside the band, bit 1 = one above it
 
     const int tid = threadIdx.x;
     const int tx = tid % T::TX, ty = tid / T::TX;
@@ -218,7 +227,7 @@ gemm_kernel(const GemmParams p) {
         }
     }
 
-    if (MODE == kPam && tid < 12) stats[tid >> 2][tid & 3] = (tid & 1) ? 0 : 0x7fffffff;   // [min, max, min, max]
+    if (MODE == kPam && tid < 3) flags[tid] = 0;
 
     // Two equivalent forms of the product's integer add.  Default: the A slab is pre-biased while it
     // is staged, so a product is a two-input add.  PAMK_IADD3: operands stay raw and the bias is the
@@ -239,18 +248,13 @@ gemm_kernel(const GemmParams p) {
     };
     auto stage_store = [&](int buf, int slot) {
         if (MODE == kPam && !PAMK_EXPERIMENT_NOSTATS) {
-            int lo_a, hi_a, lo_b, hi_b;
-            minmax_bits(ra, lo_a, hi_a);
-            minmax_bits(rb, lo_b, hi_b);
-            lo_a = __reduce_min_sync(0xffffffffu, lo_a);
-            hi_a = __reduce_max_sync(0xffffffffu, hi_a);
-            lo_b = __reduce_min_sync(0xffffffffu, lo_b);
-            hi_b = __reduce_max_sync(0xffffffffu, hi_b);
-            if ((tid & 31) == 0) {
-                atomicMin(&stats[slot][0], lo_a);
-                atomicMax(&stats[slot][1], hi_a);
-                atomicMin(&stats[slot][2], lo_b);
-                atomicMax(&stats[slot][3], hi_b);
+            // clean warps (the common case) pay the band test and one vote; only a warp that holds
+            // an out-of-band element classifies it and reports to the slab's flag word
+            const bool out = band_excess(rb, band_excess(ra, 0u)) >= kBandSpan2;
+            if (__any_sync(0xffffffffu, out)) {
+                unsigned f = out ? (1u | above_band(ra) | above_band(rb)) : 0u;
+                f = __reduce_or_sync(0xffffffffu, f);
+                if ((tid & 31) == 0) atomicOr(&flags[slot], f);
             }
 #if !PAMK_IADD3
 #pragma unroll
@@ -262,7 +266,7 @@ gemm_kernel(const GemmParams p) {
     };
 
     if (slabs > 0) stage_load(k_begin);
-    __syncthreads();               // stats initialised
+    __syncthreads();               // flag words initialised
     if (slabs > 0) stage_store(0, 0);
     __syncthreads();
 
@@ -272,10 +276,10 @@ gemm_kernel(const GemmParams p) {
         if (more) stage_load(k_begin + (s + 1) * BK);
         int path = kFast;
         if (MODE == kPam && !PAMK_EXPERIMENT_NOSTATS) {
-            const int slot = s % 3;
-            path = classify(stats[slot][0], stats[slot][1], stats[slot][2], stats[slot][3]);
+            const unsigned f = flags[s % 3];
+            path = f == 0 ? kFast : ((f & 2u) ? kFull : kFlush);
             // the slot two slabs ahead was last read before the previous barrier: reset it now
-            if (tid < 4) stats[(s + 2) % 3][tid] = (tid & 1) ? 0 : 0x7fffffff;
+            if (tid == 0) flags[(s + 2) % 3] = 0;
         }
         const float* as = As[buf];
         const float* bs = Bs[buf];
