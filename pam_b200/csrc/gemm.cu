@@ -130,6 +130,42 @@ __device__ __forceinline__ void load_slab(float (&r)[NT * 4], const MatArg& m, c
     }
 }
 
+// Vectorised loads keep one pointer per task that walks along K, so the per-slab work is the load,
+// the range predicate and one pointer increment; the row clamp and the 64-bit address arithmetic
+// are done once per kernel.
+template <class T, int R, int NT, bool KC>
+struct SlabWalker {
+    const float* ptr[NT];
+    int step;                                        // elements to advance per slab
+
+    __device__ __forceinline__ void init(const MatArg& m, const float* base, int row0, int rows, int k_begin, int tid) {
+        step = KC ? T::BK : T::BK * (int)m.sk;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const int id = tid + t * T::kThreads;
+            if (KC) {
+                int row = row0 + id / (T::BK / 4);
+                row = row < rows ? row : rows - 1;
+                ptr[t] = base + (int64_t)row * m.sr + k_begin + (id % (T::BK / 4)) * 4;
+            } else {
+                const int c0 = row0 + (id % (R / 4)) * 4;
+                ptr[t] = base + (int64_t)(k_begin + id / (R / 4)) * m.sk + (c0 < rows ? c0 : rows - 4);
+            }
+        }
+    }
+
+    __device__ __forceinline__ void load(float (&r)[NT * 4], int k0, int k_end, int tid) {
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const int id = tid + t * T::kThreads;
+            const int k = KC ? k0 + (id % (T::BK / 4)) * 4 : k0 + id / (R / 4);
+            const float4 v = k < k_end ? __ldg(reinterpret_cast<const float4*>(ptr[t])) : make_float4(0.f, 0.f, 0.f, 0.f);
+            r[t * 4] = v.x; r[t * 4 + 1] = v.y; r[t * 4 + 2] = v.z; r[t * 4 + 3] = v.w;
+            ptr[t] += step;
+        }
+    }
+};
+
 // ---- registers -> shared, laid out [k][row] -----------------------------------------------------
 template <class T, int R, int NT, bool KC>
 __device__ __forceinline__ void store_slab(float* s, const float (&r)[NT * 4], int tid) {
@@ -242,9 +278,20 @@ gemm_kernel(const GemmParams p) {
 #define PAMK_RAW(x) i2f(iadd((x), p.bias_sub))
 #endif
     float ra[T::kTasksA * 4], rb[T::kTasksB * 4];
+    SlabWalker<T, BM, T::kTasksA, A_KC> walk_a;
+    SlabWalker<T, BN, T::kTasksB, B_KC> walk_b;
+    if constexpr (VEC) {
+        walk_a.init(p.A, Ab, m0, p.M, k_begin, tid);
+        walk_b.init(p.B, Bb, n0, p.N, k_begin, tid);
+    }
     auto stage_load = [&](int k0) {
-        load_slab<T, BM, T::kTasksA, A_KC, VEC>(ra, p.A, Ab, m0, p.M, k0, k_end, tid);
-        load_slab<T, BN, T::kTasksB, B_KC, VEC>(rb, p.B, Bb, n0, p.N, k0, k_end, tid);
+        if constexpr (VEC) {
+            walk_a.load(ra, k0, k_end, tid);
+            walk_b.load(rb, k0, k_end, tid);
+        } else {
+            load_slab<T, BM, T::kTasksA, A_KC, false>(ra, p.A, Ab, m0, p.M, k0, k_end, tid);
+            load_slab<T, BN, T::kTasksB, B_KC, false>(rb, p.B, Bb, n0, p.N, k0, k_end, tid);
+        }
     };
     auto stage_store = [&](int buf, int slot) {
         if (MODE == kPam && !PAMK_EXPERIMENT_NOSTATS) {
