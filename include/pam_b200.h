@@ -211,7 +211,11 @@ int pamk_adam_step(float* const* p, const float* const* g, float* const* m, floa
  * multiply-accumulate is made of and reports how many chain steps ran in how many milliseconds;
  * variant 0 fp32 add, 1 int32 add, 2 int add + fp add (1:1), 3 int multiply-add + fp add,
  * 4 alternating int add / multiply-add + fp add, 5 fp32 fma, 6 the checked loop's mix
- * (add, multiply, compare, predicated add).  `scratch` is one device int.  This call
+ * (add, multiply, compare, predicated add), 7 packed fp32 add (add.rn.f32x2), 8 two int adds +
+ * one packed fp add, 9 int add + int multiply-add + one packed fp add, 10 fp64 add,
+ * 11 and 12 mixes that form part of the products on the fp64 pipe (the low word of
+ * (2^52 + a) + b is a + b).  Variants 7-12 exist to show that no other instruction mix beats
+ * variant 2 on this GPU.  `scratch` is one device int.  This call
  * synchronises (CUDA events on `stream`). */
 int pamk_issue_rate(int variant, int iters, int ctas_per_sm, int* scratch, float* elapsed_ms,
                     double* chain_steps, void* stream);

@@ -35,6 +35,9 @@
 #endif
 // Timing experiment only (never set in shipped builds): skip the exponent-range bookkeeping and run
 // the two-instruction loop unconditionally, to measure what the bookkeeping costs.
+#ifndef PAMK_FAST_UNROLL
+#define PAMK_FAST_UNROLL 8
+#endif
 #ifndef PAMK_EXPERIMENT_NOSTATS
 #define PAMK_EXPERIMENT_NOSTATS 0
 #endif
@@ -72,22 +75,23 @@ struct Tile {
     static constexpr int TX = BN_ / 8;
     // float4 tasks per thread when staging one operand slab
     static constexpr int kTasksA = BM_ * BK_ / 4 / kThreads, kTasksB = BN_ * BK_ / 4 / kThreads;
-    // rows that one warp of the K-contiguous loader covers; also the column swizzle stride
-    static constexpr int kSwz = 32 / (BK_ / 4);
+    // rows that one warp of the K-contiguous loader covers
+    static constexpr int kRowsPerWarp = 32 / (BK_ / 4);
 };
 using TileLarge = Tile<128, 128, 16, 2>;
 using TileSmall = Tile<64, 64, 8, 8>;
 
-// Shared-memory column swizzle: the group of four k rows f = k/4 is offset by f * kSwz columns so
-// that the transposing stores of a K-contiguous operand (a warp writes kSwz rows x BK/4 k-groups)
-// hit 32 distinct banks.  Groups of four columns stay contiguous for the 128-bit fragment loads.
-template <class T>
-__device__ __forceinline__ int swz(int col, int k) { return col ^ ((k >> 2) * T::kSwz); }
+// Shared-memory layout of a slab: [k][row], rows of R floats padded by four.  The padding spreads
+// the transposing stores of a K-contiguous operand (a warp writes kRowsPerWarp rows x BK/4
+// k-groups) over the banks, and keeps every fragment address a constant offset from one base so
+// that the arithmetic loops carry no address computation (an XOR swizzle measured the same speed
+// with more instructions and a few spilled registers).
+__host__ __device__ constexpr int row_stride(int R) { return R + 4; }
 
 // ---- loaders: global -> registers ---------------------------------------------------------------
 // A slab is R rows x BK k, staged as float4 "tasks"; thread t takes tasks t, t + kThreads, ...
 //   KC (operand contiguous along k: row-major A, or B given as W[N,K]):
-//       task id -> row id / (BK/4), k-group id % (BK/4): a warp reads kSwz rows x 4*BK bytes;
+//       task id -> row id / (BK/4), k-group id % (BK/4): a warp reads kRowsPerWarp rows x 4*BK bytes;
 //   otherwise (contiguous along the row index): task id -> k = id / (R/4), four rows (id % (R/4))*4:
 //       a warp reads 512 contiguous bytes of one k.
 // Rows beyond the matrix are clamped to the last valid row (their products land in outputs that
@@ -175,10 +179,10 @@ __device__ __forceinline__ void store_slab(float* s, const float (&r)[NT * 4], i
         if (KC) {
             const int row = id / (T::BK / 4), kg = (id % (T::BK / 4)) * 4;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) s[(kg + c) * R + swz<T>(row, kg)] = r[t * 4 + c];
+            for (int c = 0; c < 4; ++c) s[(kg + c) * row_stride(R) + row] = r[t * 4 + c];
         } else {
             const int k = id / (R / 4), c0 = (id % (R / 4)) * 4;
-            *reinterpret_cast<float4*>(s + k * R + swz<T>(c0, k)) = make_float4(r[t * 4], r[t * 4 + 1], r[t * 4 + 2], r[t * 4 + 3]);
+            *reinterpret_cast<float4*>(s + k * row_stride(R) + c0) = make_float4(r[t * 4], r[t * 4 + 1], r[t * 4 + 2], r[t * 4 + 3]);
         }
     }
 }
@@ -224,8 +228,9 @@ template <int MODE, class T, bool A_KC, bool B_KC, bool VEC>
 __global__ void __launch_bounds__(T::kThreads, MODE == kPam || MODE == kStd ? T::kCtasPerSm : T::kCtasPerSm / 2)
 gemm_kernel(const GemmParams p) {
     constexpr int BM = T::BM, BN = T::BN, BK = T::BK;
-    __shared__ __align__(16) float As[2][BK * BM];
-    __shared__ __align__(16) float Bs[2][BK * BN];
+    constexpr int kFastUnroll = PAMK_FAST_UNROLL < BK ? PAMK_FAST_UNROLL : BK;
+    __shared__ __align__(16) float As[2][BK * row_stride(BM)];
+    __shared__ __align__(16) float Bs[2][BK * row_stride(BN)];
     __shared__ unsigned flags[3];   // per slab: bit 0 = an element outside the band, bit 1 = one above it
 
     const int tid = threadIdx.x;
@@ -332,15 +337,15 @@ gemm_kernel(const GemmParams p) {
         const float* bs = Bs[buf];
 
 #define PAMK_FRAGMENTS(kk)                                                                              \
-        const int4 a0 = *reinterpret_cast<const int4*>(as + (kk) * BM + swz<T>(ty * 4, (kk)));           \
-        const int4 a1 = *reinterpret_cast<const int4*>(as + (kk) * BM + swz<T>(ty * 4 + BM / 2, (kk)));  \
-        const int4 b0 = *reinterpret_cast<const int4*>(bs + (kk) * BN + swz<T>(tx * 4, (kk)));           \
-        const int4 b1 = *reinterpret_cast<const int4*>(bs + (kk) * BN + swz<T>(tx * 4 + BN / 2, (kk)));  \
+        const int4 a0 = *reinterpret_cast<const int4*>(as + (kk) * row_stride(BM) + ty * 4);           \
+        const int4 a1 = *reinterpret_cast<const int4*>(as + (kk) * row_stride(BM) + ty * 4 + BM / 2);  \
+        const int4 b0 = *reinterpret_cast<const int4*>(bs + (kk) * row_stride(BN) + tx * 4);           \
+        const int4 b1 = *reinterpret_cast<const int4*>(bs + (kk) * row_stride(BN) + tx * 4 + BN / 2);  \
         const int a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};                              \
         const int b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 
         if (MODE == kPam && path == kFast) {
-#pragma unroll
+#pragma unroll kFastUnroll
             for (int kk = 0; kk < BK; ++kk) {
                 PAMK_FRAGMENTS(kk)
 #pragma unroll

@@ -23,6 +23,76 @@ __global__ void __launch_bounds__(256) issue_kernel(int* out, int iters, int y, 
         x[j] = threadIdx.x * 977 + j * 131071 + 0x3f000000;
         acc[j] = 0.0f;
     }
+    if (VARIANT >= 7 && VARIANT <= 9) {
+        // packed variants: two accumulators share one 64-bit register pair and one add.rn.f32x2
+        unsigned long long acc2[kChains / 2];
+#pragma unroll
+        for (int j = 0; j < kChains / 2; ++j) acc2[j] = 0ull;
+        for (int it = 0; it < iters; ++it) {
+#pragma unroll
+            for (int j = 0; j < kChains / 2; ++j) {
+                if (VARIANT == 7) {        // packed FP32 add only
+                    asm volatile("{ .reg .b64 t; mov.b64 t, {%1, %2}; add.rn.f32x2 %0, %0, t; }"
+                                 : "+l"(acc2[j]) : "r"(x[2 * j]), "r"(x[2 * j + 1]));
+                } else if (VARIANT == 8) { // two integer adds + one packed FP32 add
+                    asm volatile("{ .reg .b64 t; add.s32 %1, %1, %3; add.s32 %2, %2, %3;\n"
+                                 "mov.b64 t, {%1, %2}; add.rn.f32x2 %0, %0, t; }"
+                                 : "+l"(acc2[j]), "+r"(x[2 * j]), "+r"(x[2 * j + 1]) : "r"(y));
+                } else {                   // integer add + integer multiply-add + one packed FP32 add
+                    asm volatile("{ .reg .b64 t; add.s32 %1, %1, %3; mad.lo.s32 %2, %2, %4, %3;\n"
+                                 "mov.b64 t, {%1, %2}; add.rn.f32x2 %0, %0, t; }"
+                                 : "+l"(acc2[j]), "+r"(x[2 * j]), "+r"(x[2 * j + 1]) : "r"(y), "r"(one));
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kChains / 2; ++j) {
+            acc[2 * j] = __int_as_float((int)(acc2[j] & 0xffffffffull));
+            acc[2 * j + 1] = __int_as_float((int)(acc2[j] >> 32));
+        }
+        iters = 0;
+    }
+    if (VARIANT >= 10) {
+        // variants that form some products on the FP64 pipe: the double (2^52 + a) + b has a + b
+        // (mod 2^32) in its low word
+        double d[kChains / 2];
+        unsigned long long acc2[kChains / 4];
+#pragma unroll
+        for (int j = 0; j < kChains / 2; ++j) d[j] = 4503599627370496.0 + (double)(unsigned)x[j];
+#pragma unroll
+        for (int j = 0; j < kChains / 4; ++j) acc2[j] = 0ull;
+        const double yd = (double)y;
+        for (int it = 0; it < iters; ++it) {
+            if (VARIANT == 10) {           // FP64 add only (kChains / 2 per trip, counted as such)
+#pragma unroll
+                for (int j = 0; j < kChains / 2; ++j) asm volatile("add.rn.f64 %0, %0, %1;" : "+d"(d[j]) : "d"(yd));
+            } else if (VARIANT == 11) {    // per 4 products: 2 iadd + 1 packed fadd, 2 dadd + 2 fadd
+#pragma unroll
+                for (int j = 0; j < kChains / 4; ++j) {
+                    asm volatile("{ .reg .b64 t; add.s32 %1, %1, %3; add.s32 %2, %2, %3;\n"
+                                 "mov.b64 t, {%1, %2}; add.rn.f32x2 %0, %0, t; }"
+                                 : "+l"(acc2[j]), "+r"(x[2 * j]), "+r"(x[2 * j + 1]) : "r"(y));
+                    asm volatile("{ .reg .b32 lo, hi; add.rn.f64 %1, %1, %2; mov.b64 {lo, hi}, %1;\n"
+                                 "add.rn.f32 %0, %0, lo; }" : "+f"(acc[2 * j]), "+d"(d[2 * j]) : "d"(yd));
+                    asm volatile("{ .reg .b32 lo, hi; add.rn.f64 %1, %1, %2; mov.b64 {lo, hi}, %1;\n"
+                                 "add.rn.f32 %0, %0, lo; }" : "+f"(acc[2 * j + 1]), "+d"(d[2 * j + 1]) : "d"(yd));
+                }
+            } else {                       // per 2 products: iadd + fadd, dadd + fadd
+#pragma unroll
+                for (int j = 0; j < kChains / 2; ++j) {
+                    asm volatile("add.s32 %0, %0, %1;" : "+r"(x[j]) : "r"(y));
+                    asm volatile("add.rn.f32 %0, %0, %1;" : "+f"(acc[j]) : "f"(__int_as_float(x[j])));
+                    asm volatile("{ .reg .b32 lo, hi; add.rn.f64 %1, %1, %2; mov.b64 {lo, hi}, %1;\n"
+                                 "add.rn.f32 %0, %0, lo; }" : "+f"(acc[kChains / 2 + j]), "+d"(d[j]) : "d"(yd));
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kChains / 2; ++j) x[j] ^= (int)__double2loint(d[j]);
+#pragma unroll
+        for (int j = 0; j < kChains / 4; ++j) acc[j] += __int_as_float((int)(acc2[j] & 0xffffffffull)) + __int_as_float((int)(acc2[j] >> 32));
+        iters = 0;
+    }
     for (int it = 0; it < iters; ++it) {
 #pragma unroll
         for (int j = 0; j < kChains; ++j) {
@@ -73,13 +143,14 @@ using namespace pamk;
 extern "C" {
 
 // Runs variant `variant` (0 fadd, 1 iadd, 2 iadd+fadd, 3 imad+fadd, 4 mixed-int+fadd, 5 ffma,
-// 6 checked-loop mix) for `iters` trips and writes the elapsed milliseconds and the number of
+// 6 checked-loop mix, 7 packed fadd (add.rn.f32x2), 8 two iadd + one packed fadd, 9 iadd + imad +
+// one packed fadd) for `iters` trips and writes the elapsed milliseconds and the number of
 // chain steps executed (threads x chains x iters; one step is one multiply-accumulate's worth of
 // instructions for the mixed variants).  `scratch` is a device int.  Unlike the other entry
 // points this one synchronises: it times the launch with CUDA events on `stream`.
 int pamk_issue_rate(int variant, int iters, int ctas_per_sm, int* scratch, float* elapsed_ms,
                     double* chain_steps, void* stream) {
-    if (variant < 0 || variant > 6 || iters <= 0 || ctas_per_sm <= 0 || ctas_per_sm > 8 || !scratch ||
+    if (variant < 0 || variant > 12 || iters <= 0 || ctas_per_sm <= 0 || ctas_per_sm > 8 || !scratch ||
         !elapsed_ms || !chain_steps)
         return PAMK_ERR_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -89,8 +160,9 @@ int pamk_issue_rate(int variant, int iters, int ctas_per_sm, int* scratch, float
     if (err != cudaSuccess) return record_cuda_error(err);
     err = cudaEventCreate(&e1);
     if (err != cudaSuccess) { cudaEventDestroy(e0); return record_cuda_error(err); }
-    void (*fn[7])(int*, int, int, cudaStream_t) = {launch<0>, launch<1>, launch<2>, launch<3>,
-                                                    launch<4>, launch<5>, launch<6>};
+    void (*fn[13])(int*, int, int, cudaStream_t) = {launch<0>, launch<1>, launch<2>, launch<3>, launch<4>,
+                                                     launch<5>, launch<6>, launch<7>, launch<8>, launch<9>,
+                                                     launch<10>, launch<11>, launch<12>};
     fn[variant](scratch, grid, iters, st);           // warm-up at full length: clocks settle under this load
     cudaEventRecord(e0, st);
     fn[variant](scratch, grid, iters, st);
@@ -100,7 +172,7 @@ int pamk_issue_rate(int variant, int iters, int ctas_per_sm, int* scratch, float
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
     if (err != cudaSuccess) return record_cuda_error(err);
-    *chain_steps = (double)grid * 256.0 * kChains * (double)iters;
+    *chain_steps = (double)grid * 256.0 * (variant == 10 ? kChains / 2 : kChains) * (double)iters;
     return check_launch();
 }
 
