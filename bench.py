@@ -42,7 +42,8 @@ def parse():
     ap.add_argument("--case", default=None,
                     help="run one kernel in isolation (for profiling) instead of the benchmark: "
                          "gemm | gemm_specials | deit_gemms | mul | layer_norm_fwd | layer_norm_bwd | "
-                         "softmax_fwd | softmax_bwd | adam")
+                         "softmax_fwd | softmax_bwd | adam; or a full training step, also under torchrun "
+                         "with --gpus N: deit_step | transformer_step")
     ap.add_argument("--size", type=int, default=4096, help="--case size: GEMM edge, or log2 of the element count")
     ap.add_argument("--reps", type=int, default=2)
     return ap.parse_args()
@@ -396,6 +397,73 @@ def run_case(args):
     print(json.dumps({"case": args.case, "size": n, "ms": ms, f"G{unit}_per_s": work / ms / 1e6}))
 
 
+# ---- full training steps (BASELINE configs 3 and 4) -----------------------------------------------------
+
+def run_step_case(args):
+    """One data-parallel training step per iteration: batch upload, forward, backward, gradient
+    all-reduce over the ranks (NCCL; summed, as the reference's fairseq path leaves them), fused PAM
+    Adam.  Every rank holds the same parameters and its own batch (seed + rank).  Prints the step
+    time (slowest rank, CUDA events) and the PAM multiply-accumulate rate of the whole job."""
+    import torch.distributed as dist
+    import pam_b200 as pam
+    from pam_b200 import _lib, optim, parallel, steps
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    kw = dict(approx_bwd=True)
+    g = torch.Generator().manual_seed(1000 + rank)
+    if args.case == "deit_step":
+        cfg, batch = steps.DeitConfig(), 64
+        params = steps.to_device(steps.deit_params(cfg, torch.Generator().manual_seed(5)), dev)
+        host = (torch.randn(batch, cfg.channels, cfg.image, cfg.image, generator=g).pin_memory(),
+                torch.randint(0, cfg.classes, (batch,), generator=g).pin_memory())
+        loss_fn = lambda images, labels: steps.deit_loss(pam, params, images, labels, cfg, kw)
+        macs, hyper = 3 * steps.deit_macs(cfg, batch), dict(lr=5e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.05)
+        what = f"DeiT-tiny step, batch {batch} per GPU"
+    else:
+        cfg = steps.TransformerConfig()
+        params = steps.to_device(steps.transformer_params(cfg, torch.Generator().manual_seed(5)), dev)
+        host = tuple(t.pin_memory() for t in steps.transformer_batch(cfg, g))
+        loss_fn = lambda src, prev, tgt: steps.transformer_loss(pam, params, src, prev, tgt, cfg, kw)
+        macs, hyper = 3 * steps.transformer_macs(cfg), dict(lr=5e-4, betas=(0.9, 0.98), eps=1e-8, weight_decay=1e-4)
+        what = "6+6 transformer step, 4096 tokens per GPU"
+    leaves = list(params.values())
+    opt = optim.Adam(leaves, opt_functional_cfg="pam", **hyper)
+    launches0 = None
+    times, losses = [], []
+    for it in range(args.warmup + args.steps):
+        if it == args.warmup:
+            launches0 = _lib.lib().pamk_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        batch_dev = [t.to(dev, non_blocking=True) for t in host]
+        opt.zero_grad(set_to_none=True)
+        loss = loss_fn(*batch_dev)
+        loss.backward()
+        parallel.all_reduce_gradients(leaves)
+        opt.step()
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= args.warmup:
+            times.append(e0.elapsed_time(e1))
+        losses.append(float(loss.detach()))
+    ms = parallel.max_over_ranks(sum(times) / len(times), dev)
+    launches = (_lib.lib().pamk_launch_count() - launches0) / max(1, args.steps)
+    if rank == 0:
+        print(json.dumps({"case": args.case, "workload": what, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                          "ms_per_step": ms, "PAM_MAC_per_s": macs * world / (ms * 1e-3), "MAC_per_step_per_gpu": macs,
+                          "library_launches_per_step": launches, "loss_first": losses[0], "loss_last": losses[-1],
+                          "params": sum(t.numel() for t in leaves)}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 # ---- CPU baseline / reference arm ---------------------------------------------------------------------
 
 def cpu_sample(args, target_seconds):
@@ -458,7 +526,9 @@ def run_reference(args):
 if __name__ == "__main__":
     a = parse()
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-    if a.case:
+    if a.case in ("deit_step", "transformer_step"):
+        run_step_case(a)
+    elif a.case:
         run_case(a)
     elif a.impl == "reference":
         run_reference(a)
