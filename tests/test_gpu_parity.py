@@ -321,7 +321,7 @@ def _sum_abs_products(K, A, B):
     return K.pam_matmul_fwd(A.abs(), B.abs()).double()
 
 
-@pytest.mark.parametrize("split", [2, 5, 16])
+@pytest.mark.parametrize("split", [2, 4, 5, 8, 16, 24])
 def test_matmul_split_k_within_tolerance(pam, K, dev, tile, split):
     """Split-K adds the same bit-exact products in a different association.  Bound for any
     order: |C - S| <= 2 * K * 2^-24 * sum|p_k|  (S the exact sum of the products)."""
