@@ -489,10 +489,13 @@ Plan plan_for(int64_t batch, int64_t M, int64_t N, int64_t K, int split_request)
         *actual = s;
         const int64_t per_sm = (tiles * s + sms - 1) / sms;
         const double warps = (double)(per_sm < T::kCtasPerSm ? per_sm : T::kCtasPerSm) * (T::kThreads / 32);
-        // measured: 16 resident warps per SM saturate the issue slots, 8 reach about 80 % of that
-        const double util = warps >= 16.0 ? 1.0 : (warps >= 8.0 ? 0.6 + 0.025 * warps : warps / 10.0);
+        // measured: 16 resident warps per SM saturate the issue slots, 14 reach about 86 % of that,
+        // 8 about 74 %
+        const double util = warps >= 16.0 ? 1.0 : (warps >= 8.0 ? 0.58 + 0.02 * warps : warps / 10.8);
         const double staging = T::BM >= 128 ? 1.0 : 1.06;    // the small tile stages twice the bytes per MAC
-        return (double)per_sm * T::BM * T::BN * (double)(chunk_slabs * T::BK) / util * staging +
+        // every CTA also pays a prologue (first loads exposed) and an epilogue worth about 16 k-steps
+        const double per_cta = (double)(chunk_slabs * T::BK) + 16.0;
+        return (double)per_sm * T::BM * T::BN * per_cta / util * staging +
                (s > 1 ? 1.1e6 : 0.0);                         // the reduction pass and its launch (~12 us)
     };
     Plan pl;
@@ -500,11 +503,15 @@ Plan plan_for(int64_t batch, int64_t M, int64_t N, int64_t K, int split_request)
     int64_t s = split_request > 0 ? split_request : 1, actual = 1;
     pl.cost = cost_of(s, &actual);
     pl.splits = (int)actual;
-    if (split_request == 0 && tiles < slots && slabs >= 8) {  // automatic: try to fill the SMs
-        int64_t want = slots / tiles;
-        if (want > slabs / 4) want = slabs / 4;              // keep at least four slabs per range
-        if (want > 64) want = 64;
-        for (int64_t cand = 2; cand <= want; cand = cand < 4 ? cand + 1 : cand * 2 > want && cand != want ? want : cand * 2) {
+    if (split_request == 0 && tiles < 2 * slots && slabs >= 8) {  // automatic: try to fill the SMs
+        int64_t limit = 2 * slots / tiles;                   // up to two full waves of CTAs
+        if (limit < 2) limit = 2;
+        if (limit > slabs / 4) limit = slabs / 4;            // keep at least four slabs per range
+        if (limit > 64) limit = 64;
+        // a fixed ladder plus the splits that fill exactly one and two waves
+        const int64_t ladder[] = {2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, slots / tiles, 2 * slots / tiles};
+        for (int64_t cand : ladder) {
+            if (cand < 2 || cand > limit) continue;
             int64_t got = 1;
             const double c = cost_of(cand, &got);
             if (c < pl.cost) { pl.cost = c; pl.splits = (int)got; }
