@@ -228,7 +228,8 @@ template <int MODE, class T, bool A_KC, bool B_KC, bool VEC>
 __global__ void __launch_bounds__(T::kThreads, MODE == kPam || MODE == kStd ? T::kCtasPerSm : T::kCtasPerSm / 2)
 gemm_kernel(const GemmParams p) {
     constexpr int BM = T::BM, BN = T::BN, BK = T::BK;
-    constexpr int kFastUnroll = PAMK_FAST_UNROLL < BK ? PAMK_FAST_UNROLL : BK;
+    // (the variant with both operands contiguous along their row index spills registers at 8)
+    constexpr int kFastUnroll = (!A_KC && !B_KC) || PAMK_FAST_UNROLL > BK ? BK : PAMK_FAST_UNROLL;
     __shared__ __align__(16) float As[2][BK * row_stride(BM)];
     __shared__ __align__(16) float Bs[2][BK * row_stride(BN)];
     __shared__ unsigned flags[3];   // per slab: bit 0 = an element outside the band, bit 1 = one above it
@@ -514,7 +515,9 @@ Plan plan_for(int64_t batch, int64_t M, int64_t N, int64_t K, int split_request)
             if (cand < 2 || cand > limit) continue;
             int64_t got = 1;
             const double c = cost_of(cand, &got);
-            if (c < pl.cost) { pl.cost = c; pl.splits = (int)got; }
+            // a split has to promise 5 % before it replaces the unsplit product (which also keeps
+            // the reference's summation order)
+            if (c < (pl.splits == 1 ? 0.95 * pl.cost : pl.cost)) { pl.cost = c; pl.splits = (int)got; }
         }
     }
     return pl;
