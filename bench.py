@@ -41,7 +41,7 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--case", default=None,
                     help="run one kernel in isolation (for profiling) instead of the benchmark: "
-                         "gemm | gemm_specials | deit_gemms | mul | layer_norm_fwd | layer_norm_bwd | "
+                         "gemm | gemm_specials | deit_gemms | deit_gemms_exact | mul | layer_norm_fwd | layer_norm_bwd | "
                          "softmax_fwd | softmax_bwd | adam; or a full training step, also under torchrun "
                          "with --gpus N: deit_step | transformer_step")
     ap.add_argument("--size", type=int, default=4096, help="--case size: GEMM edge, or log2 of the element count")
@@ -348,6 +348,14 @@ def run_case(args):
                 cb._matmul(0, G, W, 1.0, 2)
                 cb._matmul(0, X.T, G, 1.0, 2)
         work, unit = float(MACS_PER_STEP), "MAC"
+    elif args.case == "deit_gemms_exact":      # the eight exact-gradient products of the linear-layer set
+        d = make_inputs(1234, device=dev)
+
+        def fn():
+            for X, W, G in zip(d["X"], d["W"], d["G"]):
+                cb._matmul_bwd(G, W, X, True, 1.0, 2)            # dX[i,k] = sum_n G[i,n] * slope(X[i,k], W[n,k])
+                cb._matmul_bwd(X.T, G, W.T, False, 1.0, 2)       # dW^T[k,n] = sum_i G[i,n] * slope(W[n,k], X[i,k])
+        work, unit = float(MACS_PER_STEP) * 2 / 3, "MAC"
     elif args.case == "mul":
         count = 1 << n if n < 40 else n
         a, b = torch.randn(count, device=dev), torch.randn(count, device=dev)

@@ -142,13 +142,17 @@ int pamk_matmul_static_scratch(const float* A, const float* B, float* C,
 
 /* Exact-gradient product: out[z][i][j] = sum_k pam_bwd(D[z][i][j], other, delta) with
  * (other, delta) = (R[k][j], L[i][k]) if delta_l else (L[i][k], R[k][j]).
- * Replaces pam_matmul_bwd / pam_bmm_bwd: pam_matmul_bwd_caller, cuda_kernels.cu:834-927. */
+ * Replaces pam_matmul_bwd / pam_bmm_bwd: pam_matmul_bwd_caller, cuda_kernels.cu:834-927.
+ * split_k, workspace, workspace_bytes: as for pamk_matmul (1 = the reference's summation order;
+ * a weight gradient, whose K is the token count, needs a split to fill the GPU); scratch size from
+ * pamk_matmul_workspace_bytes, automatic choice from pamk_matmul_bwd_auto_split. */
 int pamk_matmul_bwd(const float* L, const float* R, const float* D, float* out,
                     int64_t batch, int64_t M, int64_t N, int64_t K,
                     int64_t sLb, int64_t sLm, int64_t sLk,
                     int64_t sRb, int64_t sRk, int64_t sRn,
                     int64_t sDb, int64_t sDm, int64_t sDn,
-                    int delta_l, float offset, void* stream);
+                    int delta_l, float offset, int split_k, void* workspace, size_t workspace_bytes, void* stream);
+int pamk_matmul_bwd_auto_split(int64_t batch, int64_t M, int64_t N, int64_t K);
 
 /* ---- fused layer normalisation (pam_ln) -----------------------------------------------------------
  * Replaces the chain of launches that pam/pam_ops.py:350-378 (layer_norm) issues through

@@ -477,11 +477,14 @@ struct Plan {
 };
 
 template <class T>
-Plan plan_for(int64_t batch, int64_t M, int64_t N, int64_t K, int split_request) {
+Plan plan_for(int mode, int64_t batch, int64_t M, int64_t N, int64_t K, int split_request) {
+    // the exact-gradient kernels hold a second 8x8 block of per-output constants in registers, so
+    // half as many of their CTAs fit on an SM
+    const int ctas_per_sm = mode == kBwdL || mode == kBwdR ? T::kCtasPerSm / 2 : T::kCtasPerSm;
     const int64_t sms = sm_count();
     const int64_t tiles = batch * ((M + T::BM - 1) / T::BM) * ((N + T::BN - 1) / T::BN);
     const int64_t slabs = (K + T::BK - 1) / T::BK;
-    const int64_t slots = sms * T::kCtasPerSm;
+    const int64_t slots = sms * ctas_per_sm;
     // cost of cutting K into s ranges, in multiply-accumulates per SM at full issue rate
     auto cost_of = [&](int64_t s, int64_t* actual) {
         if (s > slabs) s = slabs;
@@ -489,7 +492,7 @@ Plan plan_for(int64_t batch, int64_t M, int64_t N, int64_t K, int split_request)
         s = (slabs + chunk_slabs - 1) / chunk_slabs;         // drop ranges that would be empty
         *actual = s;
         const int64_t per_sm = (tiles * s + sms - 1) / sms;
-        const double warps = (double)(per_sm < T::kCtasPerSm ? per_sm : T::kCtasPerSm) * (T::kThreads / 32);
+        const double warps = (double)(per_sm < ctas_per_sm ? per_sm : ctas_per_sm) * (T::kThreads / 32);
         // measured: 16 resident warps per SM saturate the issue slots, 14 reach about 86 % of that,
         // 8 about 74 %
         const double util = warps >= 16.0 ? 1.0 : (warps >= 8.0 ? 0.58 + 0.02 * warps : warps / 10.8);
@@ -527,9 +530,9 @@ Plan plan_for(int64_t batch, int64_t M, int64_t N, int64_t K, int split_request)
 int g_tile_policy = 0;
 
 Plan make_plan(int mode, int64_t batch, int64_t M, int64_t N, int64_t K, int split_request) {
-    const Plan large = plan_for<TileLarge>(batch, M, N, K, split_request);
-    if (mode != kPam || g_tile_policy == 1) return large;    // the other products use the large tile
-    const Plan small = plan_for<TileSmall>(batch, M, N, K, split_request);
+    const Plan large = plan_for<TileLarge>(mode, batch, M, N, K, split_request);
+    if (mode == kStd || g_tile_policy == 1) return large;    // the true-multiply product uses the large tile
+    const Plan small = plan_for<TileSmall>(mode, batch, M, N, K, split_request);
     if (g_tile_policy == 2) return small;
     return small.cost < large.cost ? small : large;
 }
@@ -572,8 +575,14 @@ int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspa
                           : dispatch<kPam, TileLarge>(p, a_kc, b_kc, vec, grid, st);
             break;
         case kStd: rc = dispatch<kStd, TileLarge>(p, a_kc, b_kc, vec, grid, st); break;
-        case kBwdL: rc = dispatch<kBwdL, TileLarge>(p, a_kc, b_kc, vec, grid, st); break;
-        default: rc = dispatch<kBwdR, TileLarge>(p, a_kc, b_kc, vec, grid, st); break;
+        case kBwdL:
+            rc = pl.small ? dispatch<kBwdL, TileSmall>(p, a_kc, b_kc, vec, grid, st)
+                          : dispatch<kBwdL, TileLarge>(p, a_kc, b_kc, vec, grid, st);
+            break;
+        default:
+            rc = pl.small ? dispatch<kBwdR, TileSmall>(p, a_kc, b_kc, vec, grid, st)
+                          : dispatch<kBwdR, TileLarge>(p, a_kc, b_kc, vec, grid, st);
+            break;
     }
     if (rc != PAMK_OK || pl.splits == 1) return rc;
     const int64_t blocks = (count + 255) / 256;
@@ -645,6 +654,11 @@ int pamk_matmul_auto_split(int64_t batch, int64_t M, int64_t N, int64_t K) {
     return make_plan(kPam, batch, M, N, K, 0).splits;
 }
 
+int pamk_matmul_bwd_auto_split(int64_t batch, int64_t M, int64_t N, int64_t K) {
+    if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 1;
+    return make_plan(kBwdL, batch, M, N, K, 0).splits;
+}
+
 int pamk_matmul(int mul_kind, const float* A, const float* B, float* C,
                 int64_t batch, int64_t M, int64_t N, int64_t K,
                 int64_t sAb, int64_t sAm, int64_t sAk,
@@ -712,8 +726,9 @@ int pamk_matmul_bwd(const float* L, const float* R, const float* D, float* out,
                     int64_t sLb, int64_t sLm, int64_t sLk,
                     int64_t sRb, int64_t sRk, int64_t sRn,
                     int64_t sDb, int64_t sDm, int64_t sDn,
-                    int delta_l, float offset, void* stream) {
+                    int delta_l, float offset, int split_k, void* workspace, size_t workspace_bytes, void* stream) {
     if (!dims_ok(batch, M, N, K)) return batch < 0 || M < 0 || N < 0 || K < 0 ? PAMK_ERR_ARG : PAMK_ERR_SIZE;
+    if (split_k < 0) return PAMK_ERR_ARG;
     if (batch == 0 || M == 0 || N == 0) return PAMK_OK;
     if (out == nullptr || D == nullptr) return PAMK_ERR_ARG;
     GemmParams p{};
@@ -731,7 +746,8 @@ int pamk_matmul_bwd(const float* L, const float* R, const float* D, float* out,
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
     p.off = offset_bits(offset);
     p.bias_sub = isub(kBias, p.off);
-    return run(delta_l ? kBwdL : kBwdR, p, l_kc, r_kc, 1, nullptr, 0, static_cast<cudaStream_t>(stream));
+    return run(delta_l ? kBwdL : kBwdR, p, l_kc, r_kc, split_k, workspace, workspace_bytes,
+               static_cast<cudaStream_t>(stream));
 }
 
 }

@@ -181,7 +181,7 @@ def _matmul(kind, A, B, offset, dims, split_k=None):
     return out
 
 
-def _matmul_bwd(L, R, D, delta_l, offset, dims):
+def _matmul_bwd(L, R, D, delta_l, offset, dims, split_k=None):
     device = _lib.require_cuda(L, R, D)
     L, sl = _matrix(L, dims)
     R, sr = _matrix(R, dims)
@@ -192,10 +192,17 @@ def _matmul_bwd(L, R, D, delta_l, offset, dims):
     if R.shape[-2] != K or tuple(D.shape[-2:]) != (M, N):
         raise ValueError(f"shape mismatch: {tuple(L.shape)} x {tuple(R.shape)} vs {tuple(D.shape)}")
     out = torch.empty((batch, M, N) if dims == 3 else (M, N), dtype=torch.float32, device=device)
+    handle = _lib.lib()
+    if split_k is None:
+        split_k = 1 if _strict_k_order else handle.pamk_matmul_bwd_auto_split(batch, M, N, K)
+    ws_ptr, ws_bytes = None, 0
+    if split_k > 1:
+        ws_bytes = handle.pamk_matmul_workspace_bytes(batch, M, N, split_k)
+        ws_ptr = _workspace(device, ws_bytes).data_ptr()
     with _lib.device_guard(device):
-        status = _lib.lib().pamk_matmul_bwd(L.data_ptr(), R.data_ptr(), D.data_ptr(), out.data_ptr(),
-                                            batch, M, N, K, *sl, *sr, *sd, int(bool(delta_l)), offset,
-                                            _lib.stream_ptr(device))
+        status = handle.pamk_matmul_bwd(L.data_ptr(), R.data_ptr(), D.data_ptr(), out.data_ptr(),
+                                        batch, M, N, K, *sl, *sr, *sd, int(bool(delta_l)), offset,
+                                        split_k, ws_ptr, ws_bytes, _lib.stream_ptr(device))
     _lib.check(status, "pamk_matmul_bwd")
     return out
 

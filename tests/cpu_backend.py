@@ -64,6 +64,7 @@ class FakeLib:
     def pamk_pa_log_bwd(self, x, dy, dx, n, base, offset, s): return self._unary("orc_pa_log_bwd", (x, dy, dx), n, base, offset)
 
     def pamk_matmul_auto_split(self, batch, M, N, K): return 1
+    def pamk_matmul_bwd_auto_split(self, batch, M, N, K): return 1
     def pamk_matmul_workspace_bytes(self, batch, M, N, split): return 0
 
     def pamk_matmul(self, kind, A, B, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, offset, split, ws, wsb, s):
@@ -75,7 +76,7 @@ class FakeLib:
         return 0
 
     def pamk_matmul_bwd(self, L, R, D, C, batch, M, N, K, *rest):
-        strides, (delta_l, offset, _s) = rest[:9], rest[9:]
+        strides, (delta_l, offset, _split, _ws, _wsb, _s) = rest[:9], rest[9:]
         self.calls.append(("matmul_bwd", (batch, M, N, K), strides, delta_l))
         self.o.orc_matmul_bwd(L, R, D, C, batch, M, N, K, *strides, delta_l, pam_oracle.offset_to_int(offset))
         return 0

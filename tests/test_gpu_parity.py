@@ -340,6 +340,26 @@ def test_matmul_split_k_within_tolerance(pam, K, dev, tile, split):
     assert torch.equal(got, again)
 
 
+@pytest.mark.parametrize("split", [2, 7, 32])
+@pytest.mark.parametrize("delta_l", [True, False])
+def test_exact_gradient_split_k_within_tolerance(pam, K, dev, tile, split, delta_l):
+    """The exact-gradient product with K split (weight gradients contract over the token count):
+    the same bit-exact terms delta * slope, added in a different association."""
+    from pam_b200 import cuda_bindings as cb
+    g = torch.Generator().manual_seed(split + 10 * delta_l)
+    M, N, Kdim = 70, 90, 2000
+    L, R, D = torch.randn(M, Kdim, generator=g), torch.randn(Kdim, N, generator=g), torch.randn(M, N, generator=g)
+    seq = K.pam_matmul_bwd(L, R, D, True, True, delta_l, 1.0)
+    got = cb._matmul_bwd(L.to(dev), R.to(dev), D.to(dev), delta_l, 1.0, 2, split_k=split).cpu()
+    terms = K.pam_matmul_bwd(L.abs(), R.abs(), D.abs(), True, True, delta_l, 1.0).double()     # sum of |delta * slope|
+    err = (got.double() - seq.double()).abs()
+    assert bool((err <= 4 * Kdim * 2.0 ** -24 * terms).all())
+    assert float((err / (2.0 ** -24 * terms)).max()) < 4 * math.sqrt(Kdim)
+    assert torch.equal(got, cb._matmul_bwd(L.to(dev), R.to(dev), D.to(dev), delta_l, 1.0, 2, split_k=split).cpu())
+    # split_k = 1 is the reference's order
+    assert_bits_equal(cb._matmul_bwd(L.to(dev), R.to(dev), D.to(dev), delta_l, 1.0, 2, split_k=1), seq, "unsplit")
+
+
 def test_config1_matmul_forward_and_approx_backward(pam, K, dev):
     """BASELINE config 1: A[512x1024] . B[1024x512], N(0,1), forward plus approx_bwd backward with
     N(0,1) grad_out; per-product results on a sampled block and all three products bit-exact."""
