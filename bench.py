@@ -46,6 +46,8 @@ def parse():
                          "with --gpus N: deit_step | transformer_step")
     ap.add_argument("--size", type=int, default=4096, help="--case size: GEMM edge, or log2 of the element count")
     ap.add_argument("--reps", type=int, default=2)
+    ap.add_argument("--exact-bwd", action="store_true",
+                    help="training-step cases: exact piecewise-affine gradients (approx_bwd=False) instead of approx_bwd=True")
     return ap.parse_args()
 
 
@@ -427,7 +429,7 @@ def run_step_case(args):
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    kw = dict(approx_bwd=True)
+    kw = dict(approx_bwd=not args.exact_bwd)
     g = torch.Generator().manual_seed(1000 + rank)
     if args.case == "deit_step":
         cfg, batch = steps.DeitConfig(), 64
@@ -470,7 +472,7 @@ def run_step_case(args):
     ms = parallel.max_over_ranks(sum(times) / len(times), dev)
     launches = (_lib.lib().pamk_launch_count() - launches0) / max(1, args.steps)
     if rank == 0:
-        print(json.dumps({"case": args.case, "workload": what, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        print(json.dumps({"case": args.case, "workload": what, "approx_bwd": not args.exact_bwd, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                           "ms_per_step": ms, "PAM_MAC_per_s": macs * world / (ms * 1e-3), "MAC_per_step_per_gpu": macs,
                           "library_launches_per_step": launches, "loss_first": losses[0], "loss_last": losses[-1],
                           "params": sum(t.numel() for t in leaves)}))

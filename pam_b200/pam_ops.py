@@ -116,13 +116,25 @@ def _conv_geometry(X, W, stride, padding, dilation):
     return padding, stride, H_out, W_out
 
 
+def _patches(X, kernel, padding, stride, dilation, H_out, W_out):
+    """[N * locations, C*kH*kW] matrix of the receptive fields, columns ordered (channel, row,
+    column) like F.unfold.  Non-overlapping patches (stride = kernel, no padding or dilation: a
+    ViT patch embedding) are a reshape and one permuted copy, whose backward is again a permuted
+    copy; the general case goes through unfold, whose backward is a scatter-add (fold)."""
+    N, C, H, Wd = X.shape
+    kH, kW = kernel
+    if stride == kernel and padding == (0, 0) and dilation == (1, 1) and H == H_out * kH and Wd == W_out * kW:
+        return X.reshape(N, C, H_out, kH, W_out, kW).permute(0, 2, 4, 1, 3, 5).reshape(N * H_out * W_out, C * kH * kW)
+    cols = torch.nn.functional.unfold(X, kernel, padding=padding, stride=stride, dilation=dilation)
+    return cols.transpose(1, 2).reshape(-1, cols.shape[1])
+
+
 def conv2d(X, W, bias=None, stride=1, padding=0, dilation=1, *, offset=None, approx_bwd=False, use_kernel=True):
     """Convolution as unfold + PAM linear (pam/pam_ops.py:118-161)."""
     N = X.shape[0]
     C_out, _, kH, kW = W.shape
     padding, stride, H_out, W_out = _conv_geometry(X, W, stride, padding, dilation)
-    cols = torch.nn.functional.unfold(X, (kH, kW), padding=padding, stride=stride, dilation=dilation)
-    patches = cols.transpose(1, 2).reshape(-1, cols.shape[1])          # [N * locations, C*kH*kW]
+    patches = _patches(X, (kH, kW), padding, stride, _pair(dilation), H_out, W_out)
     Y = linear(patches, W.view(C_out, -1), offset=offset, approx_bwd=approx_bwd)
     Y = Y.view(N, -1, C_out).transpose(1, 2).reshape(N, C_out, H_out, W_out)
     return Y if bias is None else Y + bias.view(1, -1, 1, 1)

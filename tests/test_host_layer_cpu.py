@@ -102,3 +102,27 @@ def test_conv_power_of_two_equivalence(backend):
     conv = pam.Conv2d(5, 7, (3, 5), padding="same", approx_bwd=True)
     assert conv(torch.randn(2, 5, 6, 6, generator=g)).shape == (2, 7, 6, 6)
     assert repr(conv).startswith("pam.Conv2d(5, 7")
+
+
+def test_patch_convolution_without_unfold_equals_unfold_route(backend):
+    """Non-overlapping patches (stride = kernel: a ViT patch embedding) skip F.unfold; values and
+    gradients must be those of the reference's unfold + linear route (pam/pam_ops.py:118-161)."""
+    g = torch.Generator().manual_seed(8)
+    X = torch.randn(2, 3, 32, 48, generator=g)
+    W = torch.randn(5, 3, 16, 16, generator=g) * 0.1
+    b = torch.randn(5, generator=g)
+    gy = torch.randn(2, 5, 2, 3, generator=g)
+
+    def unfold_route(x, w, bias):
+        cols = torch.nn.functional.unfold(x, (16, 16), stride=16)
+        y = pam.linear(cols.transpose(1, 2).reshape(-1, cols.shape[1]), w.view(5, -1), approx_bwd=True)
+        return y.view(2, -1, 5).transpose(1, 2).reshape(2, 5, 2, 3) + bias.view(1, -1, 1, 1)
+
+    outs = []
+    for route in (lambda x, w, bias: pam.conv2d(x, w, bias, stride=16, approx_bwd=True), unfold_route):
+        x, w, bias = (t.clone().requires_grad_() for t in (X, W, b))
+        y = route(x, w, bias)
+        y.backward(gy)
+        outs.append((y.detach(), x.grad, w.grad, bias.grad))
+    for name, got, want in zip(("y", "dx", "dw", "db"), *outs):
+        assert torch.equal(got, want), name
