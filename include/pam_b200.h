@@ -106,6 +106,15 @@ int pamk_matmul(int mul_kind, const float* A, const float* B, float* C,
                 int64_t sAb, int64_t sAm, int64_t sAk,
                 int64_t sBb, int64_t sBk, int64_t sBn,
                 float offset, int split_k, void* workspace, size_t workspace_bytes, void* stream);
+/* pamk_matmul with an optional bias: C[z][i][j] = (sum_k ...) + bias[j], the bias added with an
+ * ordinary fp32 add after the complete sum, i.e. the same value as the reference's
+ * `matmul(X, W.T) + bias` (pam/pam_ops.py:107-115) without the extra pass over the output.
+ * bias = NULL is pamk_matmul. */
+int pamk_matmul_bias(int mul_kind, const float* A, const float* B, const float* bias, float* C,
+                     int64_t batch, int64_t M, int64_t N, int64_t K,
+                     int64_t sAb, int64_t sAm, int64_t sAk,
+                     int64_t sBb, int64_t sBk, int64_t sBn,
+                     float offset, int split_k, void* workspace, size_t workspace_bytes, void* stream);
 /* Scratch needed by pamk_matmul for a given split_k (0 for split_k <= 1). */
 size_t pamk_matmul_workspace_bytes(int64_t batch, int64_t M, int64_t N, int split_k);
 /* The split the library would choose for split_k = 0 given unlimited workspace. */
@@ -153,6 +162,14 @@ int pamk_matmul_bwd(const float* L, const float* R, const float* D, float* out,
                     int64_t sDb, int64_t sDm, int64_t sDn,
                     int delta_l, float offset, int split_k, void* workspace, size_t workspace_bytes, void* stream);
 int pamk_matmul_bwd_auto_split(int64_t batch, int64_t M, int64_t N, int64_t K);
+
+/* Column sums of a contiguous row-major [rows x cols] matrix, out[c] = sum_r X[r][c], ordinary
+ * fp32 adds in a fixed order (deterministic): the bias gradient of a linear layer, which the
+ * reference leaves to autograd's sum over the token dimension.  `workspace`: 16-byte aligned,
+ * pamk_column_sum_workspace_bytes(rows, cols) bytes. */
+size_t pamk_column_sum_workspace_bytes(int64_t rows, int64_t cols);
+int pamk_column_sum(const float* X, float* out, int64_t rows, int64_t cols, void* workspace, size_t workspace_bytes,
+                    void* stream);
 
 /* ---- fused layer normalisation (pam_ln) -----------------------------------------------------------
  * Replaces the chain of launches that pam/pam_ops.py:350-378 (layer_norm) issues through

@@ -35,6 +35,9 @@ _SIGNATURES = {
     "pamk_pa_log_fwd": (_i, [_p, _p, _i64, _f, _f, _p]),
     "pamk_pa_log_bwd": (_i, [_p, _p, _p, _i64, _f, _f, _p]),
     "pamk_matmul": (_i, [_i, _p, _p, _p] + [_i64] * 10 + [_f, _i, _p, _sz, _p]),
+    "pamk_matmul_bias": (_i, [_i, _p, _p, _p, _p] + [_i64] * 10 + [_f, _i, _p, _sz, _p]),
+    "pamk_column_sum_workspace_bytes": (_sz, [_i64, _i64]),
+    "pamk_column_sum": (_i, [_p, _p, _i64, _i64, _p, _sz, _p]),
     "pamk_matmul_workspace_bytes": (_sz, [_i64, _i64, _i64, _i]),
     "pamk_matmul_auto_split": (_i, [_i64] * 4),
     "pamk_matmul_set_tile_policy": (_i, [_i]),

@@ -59,6 +59,7 @@ struct GemmParams {
     const float* D;           // exact-gradient product only: the operand the slope depends on
     int64_t sDb, sDm, sDn;
     float* C;                 // [batch][M][N], or [split][batch][M][N] partials when splits > 1
+    const float* bias;        // optional [N]: added (ordinary fp32 add) to every output row after its sum
     int M, N, K, batch;
     int splits, k_chunk;      // K is cut into `splits` ranges of k_chunk (a multiple of the slab)
     int32_t bias_sub;         // 0x3f800000 - offset_bits
@@ -414,6 +415,15 @@ gemm_kernel(const GemmParams p) {
     // ---- epilogue ----------------------------------------------------------------------------
     float* Cz = p.C + ((int64_t)sp * p.batch + z) * ((int64_t)p.M * p.N);
     const bool vec_out = (p.N & 3) == 0 && aligned16(p.C);
+    if (p.bias != nullptr && p.splits == 1) {          // (with split-K the reduction pass adds it)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int col = n0 + tx * 4 + (j & 3) + (j >> 2) * (BN / 2);
+            const float bj = col < p.N ? __ldg(p.bias + col) : 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i][j] = fadd(acc[i][j], bj);
+        }
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int row = m0 + ty * 4 + (i & 3) + (i >> 2) * (BM / 2);
@@ -435,13 +445,15 @@ gemm_kernel(const GemmParams p) {
     }
 }
 
-// Adds the split-K partials in split order: C = ((P0 + P1) + P2) + ...
+// Adds the split-K partials in split order: C = ((P0 + P1) + P2) + ... (+ bias[column] last)
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, float* __restrict__ C,
-                                                            int64_t count, int splits) {
+                                                            int64_t count, int splits,
+                                                            const float* __restrict__ bias, int N) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
         float v = part[i];
         for (int s = 1; s < splits; ++s) v = fadd(v, part[(int64_t)s * count + i]);
+        if (bias != nullptr) v = fadd(v, __ldg(bias + (int)(i % N)));
         C[i] = v;
     }
 }
@@ -546,12 +558,12 @@ int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspa
         cudaStream_t st) {
     if (p.M == 0 || p.N == 0 || p.batch == 0) return PAMK_OK;
     const int64_t count = (int64_t)p.batch * p.M * p.N;
-    if (p.K == 0) {
+    if (p.K == 0 && p.bias == nullptr) {
         const cudaError_t e = cudaMemsetAsync(p.C, 0, count * sizeof(float), st);
         return e == cudaSuccess ? PAMK_OK : record_cuda_error(e);
     }
     if (split_k < 0) return PAMK_ERR_ARG;
-    Plan pl = make_plan(mode, p.batch, p.M, p.N, p.K, split_k);
+    Plan pl = p.K == 0 ? Plan{true, 1, 0.0} : make_plan(mode, p.batch, p.M, p.N, p.K, split_k);   // K = 0: rows of bias
     if (pl.splits > 1 && !workspace_ok(workspace, workspace_bytes, pl.splits, count)) {
         if (split_k != 0) return PAMK_ERR_WORKSPACE;         // an explicit split needs its scratch
         pl = make_plan(mode, p.batch, p.M, p.N, p.K, 1);     // automatic: fall back to no split
@@ -588,7 +600,7 @@ int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspa
     const int64_t blocks = (count + 255) / 256;
     const int64_t cap = (int64_t)sm_count() * 8;
     splitk_reduce_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, st>>>(
-        static_cast<const float*>(workspace), out, count, pl.splits);
+        static_cast<const float*>(workspace), out, count, pl.splits, p.bias, p.N);
     return check_launch();
 }
 
@@ -659,11 +671,11 @@ int pamk_matmul_bwd_auto_split(int64_t batch, int64_t M, int64_t N, int64_t K) {
     return make_plan(kBwdL, batch, M, N, K, 0).splits;
 }
 
-int pamk_matmul(int mul_kind, const float* A, const float* B, float* C,
-                int64_t batch, int64_t M, int64_t N, int64_t K,
-                int64_t sAb, int64_t sAm, int64_t sAk,
-                int64_t sBb, int64_t sBk, int64_t sBn,
-                float offset, int split_k, void* workspace, size_t workspace_bytes, void* stream) {
+int pamk_matmul_bias(int mul_kind, const float* A, const float* B, const float* bias, float* C,
+                     int64_t batch, int64_t M, int64_t N, int64_t K,
+                     int64_t sAb, int64_t sAm, int64_t sAk,
+                     int64_t sBb, int64_t sBk, int64_t sBn,
+                     float offset, int split_k, void* workspace, size_t workspace_bytes, void* stream) {
     if (mul_kind != PAMK_MUL_PAM && mul_kind != PAMK_MUL_STANDARD) return PAMK_ERR_ARG;
     if (!dims_ok(batch, M, N, K)) return batch < 0 || M < 0 || N < 0 || K < 0 ? PAMK_ERR_ARG : PAMK_ERR_SIZE;
     if (split_k < 0) return PAMK_ERR_ARG;
@@ -680,11 +692,21 @@ int pamk_matmul(int mul_kind, const float* A, const float* B, float* C,
     p.A = {A, sAb, sAm, sAk};
     p.B = {B, sBb, sBn, sBk};
     p.C = C;
+    p.bias = bias;
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
     p.off = offset_bits(offset);
     p.bias_sub = isub(kBias, p.off);
     return run(mul_kind == PAMK_MUL_PAM ? kPam : kStd, p, a_kc, b_kc, split_k, workspace, workspace_bytes,
                static_cast<cudaStream_t>(stream));
+}
+
+int pamk_matmul(int mul_kind, const float* A, const float* B, float* C,
+                int64_t batch, int64_t M, int64_t N, int64_t K,
+                int64_t sAb, int64_t sAm, int64_t sAk,
+                int64_t sBb, int64_t sBk, int64_t sBn,
+                float offset, int split_k, void* workspace, size_t workspace_bytes, void* stream) {
+    return pamk_matmul_bias(mul_kind, A, B, nullptr, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, offset, split_k,
+                            workspace, workspace_bytes, stream);
 }
 
 size_t pamk_matmul_static_scratch_bytes(void) { return kStaticScratchFloats * sizeof(float); }

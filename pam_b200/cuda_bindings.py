@@ -155,7 +155,7 @@ def _workspace(device, nbytes):
     return buf
 
 
-def _matmul(kind, A, B, offset, dims, split_k=None):
+def _matmul(kind, A, B, offset, dims, split_k=None, bias=None):
     device = _lib.require_cuda(A, B)
     A, sa = _matrix(A, dims)
     B, sb = _matrix(B, dims)
@@ -174,10 +174,31 @@ def _matmul(kind, A, B, offset, dims, split_k=None):
         ws_bytes = handle.pamk_matmul_workspace_bytes(batch, M, N, split_k)
         ws_ptr = _workspace(device, ws_bytes).data_ptr()
     with _lib.device_guard(device):
-        status = handle.pamk_matmul(kind, A.data_ptr(), B.data_ptr(), out.data_ptr(), batch, M, N, K,
-                                    sa[0], sa[1], sa[2], sb[0], sb[1], sb[2], offset, split_k,
-                                    ws_ptr, ws_bytes, _lib.stream_ptr(device))
+        if bias is None:
+            status = handle.pamk_matmul(kind, A.data_ptr(), B.data_ptr(), out.data_ptr(), batch, M, N, K,
+                                        sa[0], sa[1], sa[2], sb[0], sb[1], sb[2], offset, split_k,
+                                        ws_ptr, ws_bytes, _lib.stream_ptr(device))
+        else:
+            status = handle.pamk_matmul_bias(kind, A.data_ptr(), B.data_ptr(), bias.data_ptr(), out.data_ptr(),
+                                             batch, M, N, K, sa[0], sa[1], sa[2], sb[0], sb[1], sb[2], offset,
+                                             split_k, ws_ptr, ws_bytes, _lib.stream_ptr(device))
     _lib.check(status, "pamk_matmul")
+    return out
+
+
+def _column_sum(X):
+    """Sum over the rows of a 2-D tensor (the bias gradient of a linear layer)."""
+    device = _lib.require_cuda(X)
+    X = X.detach().float().contiguous()
+    rows, cols = X.shape
+    out = torch.empty(cols, dtype=torch.float32, device=device)
+    handle = _lib.lib()
+    ws_bytes = handle.pamk_column_sum_workspace_bytes(rows, cols)
+    ws = _workspace(device, ws_bytes) if ws_bytes else None
+    with _lib.device_guard(device):
+        status = handle.pamk_column_sum(X.data_ptr(), out.data_ptr(), rows, cols,
+                                        ws.data_ptr() if ws is not None else None, ws_bytes, _lib.stream_ptr(device))
+    _lib.check(status, "pamk_column_sum")
     return out
 
 
@@ -412,6 +433,33 @@ class _MatMul(torch.autograd.Function):
         return dA, dB, None, None, None
 
 
+class _Linear(torch.autograd.Function):
+    """X @ W.T + bias in one launch (the bias is added in the product's epilogue with the same
+    ordinary add the reference issues separately, pam/pam_ops.py:107-115); the gradients are those
+    of _MatMul for X and W.T, and the column sum of the incoming gradient for the bias."""
+
+    @staticmethod
+    def forward(ctx, X, W, bias, offset, approx):
+        ctx.save_for_backward(X, W)
+        ctx.cfg = (offset, approx)
+        return _matmul(_lib.MUL_PAM, X, W.T, offset, 2, bias=bias)
+
+    @staticmethod
+    def backward(ctx, g):
+        X, W = ctx.saved_tensors
+        offset, (approx_a, approx_b) = ctx.cfg
+        dX = dW = db = None
+        if ctx.needs_input_grad[0]:
+            dX = _matmul(_lib.MUL_PAM, g, W, offset, 2) if approx_a else _matmul_bwd(g, W, X, True, offset, 2)
+        if ctx.needs_input_grad[1]:
+            dWt = (_matmul(_lib.MUL_PAM, X.mT, g, offset, 2) if approx_b
+                   else _matmul_bwd(X.mT, g, W.T, False, offset, 2))
+            dW = dWt.T
+        if ctx.needs_input_grad[2]:
+            db = _column_sum(g)
+        return dX, dW, db, None, None
+
+
 class _StandardMatMul(torch.autograd.Function):
     @staticmethod
     def forward(ctx, A, B, bmm):
@@ -453,6 +501,12 @@ def pad(A, B, *, offset=None, approx_bwd=False):
 
 def pam_matmul(A, B, *, offset=None, approx_bwd=False):
     return _MatMul.apply(A, B, _offset(offset), _pair(approx_bwd), False)
+
+
+def pam_linear(X, W, bias, *, offset=None, approx_bwd=False):
+    """[rows, in] x [out, in] + [out] (no counterpart in the reference's bindings: its `linear` is
+    pam_matmul followed by a torch add)."""
+    return _Linear.apply(X, W, bias, _offset(offset), _pair(approx_bwd))
 
 
 def pam_bmm(A, B, *, offset=None, approx_bwd=False):

@@ -172,6 +172,17 @@ def logsumexp(x, dim, keepdim=False, *, offset=None, approx_bwd=False):
     return out.unsqueeze(-1) if keepdim else out
 
 
+# ---- linear layer with bias ----------------------------------------------------------------------------
+
+def linear_bias_supported(X2, W, bias):
+    """The bias can ride in the product's epilogue when it is a plain fp32 vector of the output width
+    on the operands' device."""
+    return (enabled and isinstance(bias, torch.Tensor) and isinstance(X2, torch.Tensor) and isinstance(W, torch.Tensor)
+            and X2.is_cuda and bias.is_cuda and W.is_cuda and bias.dtype == torch.float32 and bias.dim() == 1
+            and W.dim() == 2 and bias.shape[0] == W.shape[0] and bias.is_contiguous()
+            and X2.dtype == torch.float32 and W.dtype == torch.float32)
+
+
 # ---- Adam --------------------------------------------------------------------------------------------
 
 def adam_supported(p, grad):

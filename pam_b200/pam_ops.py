@@ -89,7 +89,11 @@ def linear(X, W, bias=None, *, offset=None, approx_bwd=False, use_kernel=True):
     """X @ W.T (+ bias with an ordinary add) over the flattened leading dimensions
     (pam/pam_ops.py:107-115).  W is [out, in]: both operands are contiguous along K."""
     lead = X.shape[:-1]
-    out = matmul(X.reshape(-1, X.shape[-1]), W.T, offset=offset, approx_bwd=approx_bwd)
+    X2 = X.reshape(-1, X.shape[-1])
+    if fused.linear_bias_supported(X2, W, bias):
+        out = cuda_bindings.pam_linear(X2, W, bias, offset=offset, approx_bwd=approx_bwd)
+        return out.reshape(*lead, out.shape[-1])
+    out = matmul(X2, W.T, offset=offset, approx_bwd=approx_bwd)
     out = out.reshape(*lead, out.shape[-1])
     return out if bias is None else out + bias
 

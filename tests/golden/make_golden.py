@@ -17,6 +17,7 @@ The Adam entries replay submodules/fairseq/fairseq/optim/adam.py:226-252 with th
 ``pam.mul/div/pow`` (fairseq itself cannot be imported here: omegaconf and friends are absent).
 """
 import math
+import os
 import pathlib
 import sys
 
@@ -24,7 +25,7 @@ import numpy as np
 import torch
 
 ROOT = pathlib.Path(__file__).resolve().parents[2]
-REF = pathlib.Path("/root/reference")
+REF = pathlib.Path(os.environ.get("PAM_REFERENCE_ROOT", "/root/reference"))
 sys.path.insert(0, str(ROOT))
 
 from oracle import build as oracle_build  # noqa: E402

@@ -16,6 +16,7 @@ Per workload the fixture holds the inputs' seed-derived tensors, the loss, every
 parameter after the update, and the loss of a second forward pass with the updated parameters.
 """
 import math
+import os
 import pathlib
 import sys
 
@@ -23,7 +24,7 @@ import numpy as np
 import torch
 
 ROOT = pathlib.Path(__file__).resolve().parents[2]
-REF = pathlib.Path("/root/reference")
+REF = pathlib.Path(os.environ.get("PAM_REFERENCE_ROOT", "/root/reference"))
 sys.path.insert(0, str(ROOT))
 
 from oracle import build as oracle_build  # noqa: E402

@@ -719,3 +719,54 @@ def test_abi_rejects_bad_arguments_on_gpu(pam, dev):
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         pam.mul(torch.ones(3), torch.ones(3))
     torch.cuda.synchronize()
+
+
+# ---- linear layer with the bias in the product's epilogue ---------------------------------------------
+
+@pytest.mark.parametrize("M,N,Kdim", [(1, 1, 1), (5, 3, 7), (64, 64, 16), (197, 130, 100), (300, 576, 192)])
+@pytest.mark.parametrize("approx", [True, False])
+def test_linear_bias_epilogue_bit_exact(pam, K, oracle, dev, tile, M, N, Kdim, approx):
+    """y = X W^T + b with the add fused into the product: the same bits as the reference's product
+    followed by a separate add; gradients of X and W as for the plain product; the bias gradient is
+    a column sum (ordinary fp32 adds, compared with a float64 sum)."""
+    g = torch.Generator().manual_seed(M * 31 + N)
+    X, W, b = torch.randn(M, Kdim, generator=g), torch.randn(N, Kdim, generator=g) * 0.1, torch.randn(N, generator=g)
+    G = torch.randn(M, N, generator=g)
+    Xd, Wd, bd = (t.to(dev).requires_grad_() for t in (X, W, b))
+    y = pam.linear(Xd, Wd, bd, approx_bwd=approx)
+    y.backward(G.to(dev))
+    assert_bits_equal(y, K.pam_matmul_fwd(X, W.T) + b, "y")
+    if approx:
+        assert_bits_equal(Xd.grad, K.pam_matmul_fwd(G, W), "dX")
+        assert_bits_equal(Wd.grad, K.pam_matmul_fwd(G.T, X), "dW")
+    else:
+        assert_bits_equal(Xd.grad, K.pam_matmul_bwd(G, W, X, True, True, True, 1.0), "dX")
+        assert_bits_equal(Wd.grad.T, K.pam_matmul_bwd(X.T, G, W.T, True, True, False, 1.0), "dW")
+    want = G.double().sum(0)
+    assert bool(((bd.grad.cpu().double() - want).abs() <= 1e-6 * G.abs().double().sum(0) + 1e-9).all())
+
+
+def test_linear_bias_with_split_k_and_empty_k(pam, K, dev, tile):
+    from pam_b200 import cuda_bindings as cb
+    g = torch.Generator().manual_seed(77)
+    X, W, b = torch.randn(40, 3000, generator=g), torch.randn(24, 3000, generator=g), torch.randn(24, generator=g)
+    plain = cb._matmul(0, X.to(dev), W.T.to(dev), 1.0, 2, split_k=6)
+    fused_ = cb._matmul(0, X.to(dev), W.T.to(dev), 1.0, 2, split_k=6, bias=b.to(dev))
+    assert_bits_equal(fused_, plain.cpu() + b, "split-K: bias added after the partial sums")
+    empty = cb._matmul(0, torch.empty(5, 0, device=dev), torch.empty(0, 24, device=dev), 1.0, 2, bias=b.to(dev))
+    assert_bits_equal(empty, (torch.zeros(5, 24) + b), "K = 0: rows of bias")
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (63, 5), (1000, 192), (12608, 768), (4096, 10000), (7, 130)])
+def test_column_sum(pam, dev, rows, cols):
+    from pam_b200 import cuda_bindings as cb
+    g = torch.Generator().manual_seed(rows + cols)
+    X = torch.randn(rows, cols, generator=g)
+    got = cb._column_sum(X.to(dev))
+    want = X.double().sum(0)
+    bound = 2.0 ** -23 * math.sqrt(rows) * X.abs().double().sum(0) + 1e-12
+    assert bool(((got.cpu().double() - want).abs() <= bound).all())
+    assert torch.equal(got, cb._column_sum(X.to(dev)))
+    # a view with a row stride is gathered first
+    wide = torch.randn(rows, cols + 3, generator=g).to(dev)
+    assert torch.equal(cb._column_sum(wide[:, :cols]), cb._column_sum(wide[:, :cols].contiguous()))
