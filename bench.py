@@ -42,7 +42,7 @@ def parse():
     ap.add_argument("--case", default=None,
                     help="run one kernel in isolation (for profiling) instead of the benchmark: "
                          "gemm | gemm_specials | deit_gemms | deit_gemms_exact | mul | layer_norm_fwd | layer_norm_bwd | "
-                         "softmax_fwd | softmax_bwd | adam; or a full training step, also under torchrun "
+                         "softmax_fwd | softmax_bwd | adam | column_sum; or a full training step, also under torchrun "
                          "with --gpus N: deit_step | transformer_step")
     ap.add_argument("--size", type=int, default=4096, help="--case size: GEMM edge, or log2 of the element count")
     ap.add_argument("--reps", type=int, default=2)
@@ -392,6 +392,10 @@ def run_case(args):
             fn = lambda: torch.autograd.grad(y, (x,), gy, retain_graph=True)
             work = 16.0 * rows * length           # maximum pass 4 B + row pass 12 B per element
         unit = "B"
+    elif args.case == "column_sum":            # bias gradient of a linear layer: 768-wide rows
+        count = 1 << n if n < 40 else n
+        x = torch.randn(count // 768, 768, device=dev)
+        fn, work, unit = (lambda: cb._column_sum(x)), 4.0 * x.numel(), "B"
     elif args.case == "adam":
         from pam_b200 import optim
         count = 1 << n if n < 40 else n
