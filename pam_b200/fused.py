@@ -178,7 +178,8 @@ def linear_bias_supported(X2, W, bias):
     """The bias can ride in the product's epilogue when it is a plain fp32 vector of the output width
     on the operands' device."""
     return (enabled and isinstance(bias, torch.Tensor) and isinstance(X2, torch.Tensor) and isinstance(W, torch.Tensor)
-            and X2.is_cuda and bias.is_cuda and W.is_cuda and bias.dtype == torch.float32 and bias.dim() == 1
+            and X2.is_cuda and bias.device == X2.device and W.device == X2.device
+            and bias.dtype == torch.float32 and bias.dim() == 1
             and W.dim() == 2 and bias.shape[0] == W.shape[0] and bias.is_contiguous()
             and X2.dtype == torch.float32 and W.dtype == torch.float32)
 
