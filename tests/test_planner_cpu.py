@@ -1,0 +1,39 @@
+"""The split-K planner of the PAM matrix product, queried without a GPU (it assumes a 148-SM device
+when none is present).  The expected splits for the DeiT-tiny linear-layer products are the ones an
+exhaustive tile x split sweep on a B200 measured fastest (within 1 %); pinning them here keeps a
+change of the cost model from silently moving the benchmark's products off their optimum."""
+import pytest
+
+from pam_b200 import _lib
+
+TOKENS = 12608
+
+
+@pytest.fixture(scope="module")
+def lib():
+    return _lib.lib()
+
+
+@pytest.mark.parametrize("M,N,K,split", [
+    (TOKENS, 576, 192, 1), (TOKENS, 192, 576, 2), (192, 576, TOKENS, 43),        # 192 -> 576: forward, dX, dW
+    (TOKENS, 192, 192, 1), (192, 192, TOKENS, 64),                              # 192 -> 192
+    (TOKENS, 768, 192, 1), (TOKENS, 192, 768, 2), (192, 768, TOKENS, 32),        # 192 -> 768 and 768 -> 192
+    (768, 192, TOKENS, 32),
+])
+def test_deit_products_keep_their_measured_best_split(lib, M, N, K, split):
+    assert lib.pamk_matmul_auto_split(1, M, N, K) == split
+
+
+def test_planner_basic_properties(lib):
+    # large outputs fill the GPU without a split; tiny K is never split; empty problems do not divide by zero
+    assert lib.pamk_matmul_auto_split(1, 4096, 4096, 4096) == 1
+    assert lib.pamk_matmul_auto_split(1, 64, 64, 16) == 1
+    assert lib.pamk_matmul_auto_split(1, 0, 64, 64) == 1 and lib.pamk_matmul_auto_split(1, 64, 64, 0) == 1
+    # a weight gradient over many tokens is split for the exact-gradient product as well
+    assert lib.pamk_matmul_bwd_auto_split(1, 192, 576, TOKENS) > 8
+    # the split never leaves a range with fewer than four slabs of 8
+    for K in (32, 64, 200, 1000, 5000):
+        s = lib.pamk_matmul_auto_split(1, 64, 64, K)
+        assert s == 1 or K / s >= 32
+    # scratch size is the split times the output
+    assert lib.pamk_matmul_workspace_bytes(2, 3, 5, 4) == 2 * 3 * 5 * 4 * 4
