@@ -79,12 +79,12 @@ struct RowRegs {
     float v[NCH * VEC];
 };
 
-template <int VEC, int NCH>
+template <int VEC, int NCH, bool FULL>
 __device__ __forceinline__ void load_row(RowRegs<VEC, NCH>& r, const float* p, int width, int lane, float fill) {
 #pragma unroll
     for (int q = 0; q < NCH; ++q) {
         const int col = (q * 32 + lane) * VEC;
-        if (col < width) {
+        if (FULL || col < width) {
             if (VEC == 4) {
                 const float4 t = __ldg(reinterpret_cast<const float4*>(p + col));
                 r.v[q * 4] = t.x; r.v[q * 4 + 1] = t.y; r.v[q * 4 + 2] = t.z; r.v[q * 4 + 3] = t.w;
@@ -101,12 +101,12 @@ __device__ __forceinline__ void load_row(RowRegs<VEC, NCH>& r, const float* p, i
     }
 }
 
-template <int VEC, int NCH>
+template <int VEC, int NCH, bool FULL>
 __device__ __forceinline__ void store_row(const RowRegs<VEC, NCH>& r, float* p, int width, int lane) {
 #pragma unroll
     for (int q = 0; q < NCH; ++q) {
         const int col = (q * 32 + lane) * VEC;
-        if (col < width) {
+        if (FULL || col < width) {
             if (VEC == 4)
                 *reinterpret_cast<float4*>(p + col) = make_float4(r.v[q * 4], r.v[q * 4 + 1], r.v[q * 4 + 2], r.v[q * 4 + 3]);
             else if (VEC == 2)
@@ -117,14 +117,16 @@ __device__ __forceinline__ void store_row(const RowRegs<VEC, NCH>& r, float* p, 
     }
 }
 
-template <int VEC, int NCH>
+// FULL: the row fills every register slot of the layout (width == 32 * VEC * NCH: 128, 192, 256,
+// 512, 768, 1024), so no column needs a bounds test.
+template <int VEC, int NCH, bool FULL>
 __device__ __forceinline__ bool live(int i, int width, int lane) {
-    return ((i / VEC) * 32 + lane) * VEC + (i % VEC) < width;
+    return FULL || ((i / VEC) * 32 + lane) * VEC + (i % VEC) < width;
 }
 
 // Forward chain up to the centred row and the row scalars.  Padding lanes hold 0 in `c` so that
 // pam(0, 0) = +0 leaves the sums untouched.
-template <int VEC, int NCH>
+template <int VEC, int NCH, bool FULL>
 __device__ __forceinline__ void centre_and_stats(RowRegs<VEC, NCH>& c, RowStats& st, const LnArgs& a,
                                                  const Shared& sh, int lane) {
     float s = 0.0f;
@@ -135,7 +137,7 @@ __device__ __forceinline__ void centre_and_stats(RowRegs<VEC, NCH>& c, RowStats&
     s = 0.0f;
 #pragma unroll
     for (int i = 0; i < NCH * VEC; ++i) {
-        c.v[i] = live<VEC, NCH>(i, a.width, lane) ? fadd(c.v[i], -st.mu) : 0.0f;
+        c.v[i] = live<VEC, NCH, FULL>(i, a.width, lane) ? fadd(c.v[i], -st.mu) : 0.0f;
         s = fadd(s, mul(c.v[i], c.v[i], a.off));
     }
     st.s2 = warp_sum(s);
@@ -148,7 +150,7 @@ constexpr int min_ctas(int slots, bool backward) {
     return slots <= 8 ? (backward ? 6 : 10) : (slots <= 16 ? (backward ? 4 : 6) : 1);
 }
 
-template <int VEC, int NCH>
+template <int VEC, int NCH, bool FULL>
 __global__ void __launch_bounds__(kThreads, min_ctas(VEC * NCH, false)) ln_fwd_kernel(const LnArgs a) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
@@ -156,29 +158,29 @@ __global__ void __launch_bounds__(kThreads, min_ctas(VEC * NCH, false)) ln_fwd_k
     const Shared sh = make_shared(a.nf, a.off);
     for (int64_t row = warp; row < a.rows; row += nwarps) {
         RowRegs<VEC, NCH> c;
-        load_row<VEC, NCH>(c, a.x + row * a.width, a.width, lane, 0.0f);
+        load_row<VEC, NCH, FULL>(c, a.x + row * a.width, a.width, lane, 0.0f);
         RowStats st;
-        centre_and_stats<VEC, NCH>(c, st, a, sh, lane);
+        centre_and_stats<VEC, NCH, FULL>(c, st, a, sh, lane);
         const Divisor by_denom = make_divisor(st.denom, a.off);
         // weight and bias are re-read per row (they stay in L1) rather than held in registers for
         // the whole kernel: the registers buy more resident warps
         RowRegs<VEC, NCH> p;
-        if (a.w) load_row<VEC, NCH>(p, a.w, a.width, lane, 1.0f);
+        if (a.w) load_row<VEC, NCH, FULL>(p, a.w, a.width, lane, 1.0f);
 #pragma unroll
         for (int i = 0; i < NCH * VEC; ++i) {
             const float y = div_by(c.v[i], by_denom);
             c.v[i] = a.w ? mul(y, p.v[i], a.off) : y;
         }
         if (a.b) {
-            load_row<VEC, NCH>(p, a.b, a.width, lane, 0.0f);
+            load_row<VEC, NCH, FULL>(p, a.b, a.width, lane, 0.0f);
 #pragma unroll
             for (int i = 0; i < NCH * VEC; ++i) c.v[i] = fadd(c.v[i], p.v[i]);
         }
-        store_row<VEC, NCH>(c, a.out + row * a.width, a.width, lane);
+        store_row<VEC, NCH, FULL>(c, a.out + row * a.width, a.width, lane);
     }
 }
 
-template <int VEC, int NCH, bool APPROX>
+template <int VEC, int NCH, bool APPROX, bool FULL>
 __global__ void __launch_bounds__(kThreads, min_ctas(VEC * NCH, true)) ln_bwd_kernel(const LnArgs a) {
     __shared__ float stage[kWarpsPerCta][NCH * VEC][32];
     const int lane = threadIdx.x & 31;
@@ -189,16 +191,16 @@ __global__ void __launch_bounds__(kThreads, min_ctas(VEC * NCH, true)) ln_bwd_ke
     const Shared sh = make_shared(a.nf, a.off);
     const float recip_n = div_by(1.0f, sh.by_n);
     RowRegs<VEC, NCH> w, dw, db;
-    if (a.w) load_row<VEC, NCH>(w, a.w, a.width, lane, 1.0f);
+    if (a.w) load_row<VEC, NCH, FULL>(w, a.w, a.width, lane, 1.0f);
 #pragma unroll
     for (int i = 0; i < NCH * VEC; ++i) dw.v[i] = db.v[i] = 0.0f;
 
     for (int64_t row = warp; row < a.rows; row += nwarps) {
         RowRegs<VEC, NCH> c, g;
-        load_row<VEC, NCH>(c, a.x + row * a.width, a.width, lane, 0.0f);
-        load_row<VEC, NCH>(g, a.dy + row * a.width, a.width, lane, 0.0f);
+        load_row<VEC, NCH, FULL>(c, a.x + row * a.width, a.width, lane, 0.0f);
+        load_row<VEC, NCH, FULL>(g, a.dy + row * a.width, a.width, lane, 0.0f);
         RowStats st;
-        centre_and_stats<VEC, NCH>(c, st, a, sh, lane);
+        centre_and_stats<VEC, NCH, FULL>(c, st, a, sh, lane);
         const Divisor by_denom = make_divisor(st.denom, a.off);
         const float recip = div_by(1.0f, by_denom);
 
@@ -206,7 +208,7 @@ __global__ void __launch_bounds__(kThreads, min_ctas(VEC * NCH, true)) ln_bwd_ke
         float sum_dden = 0.0f;
 #pragma unroll
         for (int i = 0; i < NCH * VEC; ++i) {
-            const bool on = live<VEC, NCH>(i, a.width, lane);
+            const bool on = live<VEC, NCH, FULL>(i, a.width, lane);
             const float xn = div_by(c.v[i], by_denom);
             float dxn = g.v[i];
             if (a.w) {
@@ -238,13 +240,13 @@ __global__ void __launch_bounds__(kThreads, min_ctas(VEC * NCH, true)) ln_bwd_ke
         for (int i = 0; i < NCH * VEC; ++i) {
             const float dsq = APPROX ? mul(d_s2, c.v[i], a.off) : mul_bwd(c.v[i], c.v[i], d_s2, a.off);
             g.v[i] = fadd(fadd(g.v[i], dsq), dsq);
-            if (live<VEC, NCH>(i, a.width, lane)) sum_dc = fadd(sum_dc, g.v[i]);
+            if (live<VEC, NCH, FULL>(i, a.width, lane)) sum_dc = fadd(sum_dc, g.v[i]);
         }
         const float d_mu = -warp_sum(sum_dc);
         const float d_s1 = APPROX ? mul(recip_n, d_mu, a.off) : mul_bwd(st.s1, recip_n, d_mu, 0);
 #pragma unroll
         for (int i = 0; i < NCH * VEC; ++i) g.v[i] = fadd(g.v[i], d_s1);
-        store_row<VEC, NCH>(g, a.out + row * a.width, a.width, lane);
+        store_row<VEC, NCH, FULL>(g, a.out + row * a.width, a.width, lane);
     }
 
     // per-CTA column sums for dw / db: warps are added in warp order, CTAs by the second kernel
@@ -323,8 +325,13 @@ int launch(const LnArgs& a, int grid, cudaStream_t st) {
     const bool v2 = (a.width & 1) == 0 && (bits & 7u) == 0;
 #define PAMK_LN(V, N)                                                                   \
     do {                                                                                \
-        if (BWD) ln_bwd_kernel<V, N, APPROX><<<grid, kThreads, 0, st>>>(a);             \
-        else ln_fwd_kernel<V, N><<<grid, kThreads, 0, st>>>(a);                         \
+        if (a.width == 32 * (V) * (N)) {                                                \
+            if (BWD) ln_bwd_kernel<V, N, APPROX, true><<<grid, kThreads, 0, st>>>(a);   \
+            else ln_fwd_kernel<V, N, true><<<grid, kThreads, 0, st>>>(a);               \
+        } else {                                                                        \
+            if (BWD) ln_bwd_kernel<V, N, APPROX, false><<<grid, kThreads, 0, st>>>(a);  \
+            else ln_fwd_kernel<V, N, false><<<grid, kThreads, 0, st>>>(a);              \
+        }                                                                               \
         return check_launch();                                                          \
     } while (0)
     if (v4 && a.width <= 128) PAMK_LN(4, 1);
