@@ -3,7 +3,8 @@
 // This is the bias gradient of a linear layer (the reference leaves it to autograd's sum over the
 // token dimension).  Deterministic two-pass reduction: CTAs own a tile of 128 columns and a
 // contiguous chunk of rows, their 8 warps walk the chunk with a stride of 8 rows and are added in
-// warp order; a second kernel adds the chunks in chunk order.  HBM-bound: the matrix is read once.
+// warp order; a second kernel adds the chunks (32 interleaved subsets, then those in order).
+// HBM-bound: the matrix is read once.
 #include "common.cuh"
 #include "pam_scalar.cuh"
 
@@ -49,14 +50,27 @@ __global__ void __launch_bounds__(kColWarps * 32) column_partial_kernel(const fl
     }
 }
 
-// out[c] = ((partial[0][c] + partial[1][c]) + ...) in chunk order
-__global__ void __launch_bounds__(256) column_final_kernel(const float* __restrict__ partial, float* __restrict__ out,
-                                                           int chunks, int cols) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
-    float t = partial[c];
-    for (int k = 1; k < chunks; ++k) t = fadd(t, partial[(int64_t)k * cols + c]);
-    out[c] = t;
+// out[c] = sum over chunks of partial[chunk][c].  One CTA per 32 columns; warp j adds the chunks
+// j, j + 32, j + 64, ... in that order, then the 32 warp sums are added in warp order.
+constexpr int kFinalWarps = 32;
+__global__ void __launch_bounds__(kFinalWarps * 32) column_final_kernel(const float* __restrict__ partial,
+                                                                        float* __restrict__ out, int chunks, int cols) {
+    __shared__ float stage[kFinalWarps][32];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane;
+    float t = 0.0f;
+    if (c < cols) {
+#pragma unroll 4
+        for (int k = wid; k < chunks; k += kFinalWarps) t = fadd(t, __ldg(partial + (int64_t)k * cols + c));
+    }
+    stage[wid][lane] = t;
+    __syncthreads();
+    if (wid == 0 && c < cols) {
+        t = stage[0][lane];
+#pragma unroll
+        for (int k = 1; k < kFinalWarps; ++k) t = fadd(t, stage[k][lane]);
+        out[c] = t;
+    }
 }
 
 // Row chunks: enough CTAs for about four per SM, at least 64 rows each.
@@ -105,7 +119,7 @@ int pamk_column_sum(const float* X, float* out, int64_t rows, int64_t cols, void
         column_partial_kernel<false><<<grid, kColWarps * 32, 0, st>>>(X, partial, rows, (int)cols, rows_per_chunk);
     int rc = check_launch();
     if (rc != PAMK_OK) return rc;
-    column_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(partial, out, chunks, (int)cols);
+    column_final_kernel<<<(unsigned)((cols + 31) / 32), kFinalWarps * 32, 0, st>>>(partial, out, chunks, (int)cols);
     return check_launch();
 }
 
