@@ -23,7 +23,6 @@ import math
 import pathlib
 import struct
 
-import numpy as np
 import torch
 
 _HERE = pathlib.Path(__file__).resolve().parent

@@ -16,7 +16,7 @@ import math
 
 import torch
 
-from . import _lib, utils
+from . import _lib
 from ._lib import COL, FULL, IMM, ROW, SCALAR
 
 # When True, matrix products never split K: every output is summed strictly in k order and the

@@ -7,7 +7,6 @@ PAM linear factory, both attention products through the PAM bmm, timm/models/vis
 update rule).  Sizes are DeiT-tiny's (197 tokens, d = 192, 3 heads, MLP 768) with a small batch;
 approx_bwd = True as in the configs.  Values that only differ by the association of fp32 sums
 (row reductions, bias gradients) are compared with a relative tolerance."""
-import math
 
 import pytest
 import torch

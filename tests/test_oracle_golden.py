@@ -6,7 +6,7 @@ import math
 import pytest
 import torch
 
-from conftest import assert_bits_equal, assert_close_nan
+from conftest import assert_bits_equal
 
 
 def test_reference_known_answers(oracle):

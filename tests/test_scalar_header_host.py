@@ -1,5 +1,4 @@
 """The shipped scalar header, compiled for the host, against the CPU oracle (no GPU needed)."""
-import pathlib
 import subprocess
 
 import pytest
