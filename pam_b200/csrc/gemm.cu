@@ -66,14 +66,16 @@ struct GemmParams {
     int32_t off;              // offset_bits
 };
 
-// Tile shapes.  Every thread owns an 8x8 micro-tile, so a CTA has BM*BN/64 threads.
+// Tile shapes.  Every thread owns a square register micro-tile (8x8 unless said otherwise).
 //   128x128x16, 256 threads, 2 CTAs/SM: least staging overhead, for large outputs;
 //   64x64x8,     64 threads, 8 CTAs/SM: four times as many CTAs, for outputs that would leave a
 //                                       large tile grid with a ragged last wave (e.g. 12608 x 192).
-template <int BM_, int BN_, int BK_, int CPS_>
+template <int BM_, int BN_, int BK_, int CPS_, int MT_ = 8>
 struct Tile {
-    static constexpr int BM = BM_, BN = BN_, BK = BK_, kThreads = BM_ * BN_ / 64, kCtasPerSm = CPS_;
-    static constexpr int TX = BN_ / 8;
+    // every thread owns an MT x MT micro-tile (8, or 4 for the tile meant for very small outputs)
+    static constexpr int BM = BM_, BN = BN_, BK = BK_, MT = MT_, kCtasPerSm = CPS_;
+    static constexpr int kThreads = (BM_ / MT_) * (BN_ / MT_);
+    static constexpr int TX = BN_ / MT_;
     // float4 tasks per thread when staging one operand slab
     static constexpr int kTasksA = BM_ * BK_ / 4 / kThreads, kTasksB = BN_ * BK_ / 4 / kThreads;
     // rows that one warp of the K-contiguous loader covers
@@ -81,6 +83,10 @@ struct Tile {
 };
 using TileLarge = Tile<128, 128, 16, 2>;
 using TileSmall = Tile<64, 64, 8, 8>;
+// 32x32x8 with a 4x4 micro-tile, 64 threads: batched products whose matrices are a fraction of a
+// 64x64 tile (attention over 32 tokens) would otherwise spend three quarters of their adds on
+// rows and columns that do not exist.
+using TileTiny = Tile<32, 32, 8, 12, 4>;
 
 // Shared-memory layout of a slab: [k][row], rows of R floats padded by four.  The padding spreads
 // the transposing stores of a K-contiguous operand (a warp writes kRowsPerWarp rows x BK/4
@@ -228,7 +234,7 @@ __device__ __forceinline__ unsigned above_band(const float (&r)[N]) {
 template <int MODE, class T, bool A_KC, bool B_KC, bool VEC>
 __global__ void __launch_bounds__(T::kThreads, MODE == kPam || MODE == kStd ? T::kCtasPerSm : T::kCtasPerSm / 2)
 gemm_kernel(const GemmParams p) {
-    constexpr int BM = T::BM, BN = T::BN, BK = T::BK;
+    constexpr int BM = T::BM, BN = T::BN, BK = T::BK, MT = T::MT;
     // (the variant with both operands contiguous along their row index spills registers at 8)
     constexpr int kFastUnroll = (!A_KC && !B_KC) || PAMK_FAST_UNROLL > BK ? BK : PAMK_FAST_UNROLL;
     __shared__ __align__(16) float As[2][BK * row_stride(BM)];
@@ -246,23 +252,23 @@ gemm_kernel(const GemmParams p) {
     const float* Ab = p.A.p + (int64_t)z * p.A.sb;
     const float* Bb = p.B.p + (int64_t)z * p.B.sb;
 
-    float acc[8][8];
+    float acc[MT][MT];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < MT; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < MT; ++j) acc[i][j] = 0.0f;
 
     // exact-gradient product: per-output constant (mantissa of D + offset) that the slope adds to
     // the other operand's bits (pam_scalar.cuh mul_slope).
-    int32_t dm[MODE >= kBwdL ? 8 : 1][MODE >= kBwdL ? 8 : 1];
+    int32_t dm[MODE >= kBwdL ? MT : 1][MODE >= kBwdL ? MT : 1];
     if constexpr (MODE >= kBwdL) {
         const float* Db = p.D + (int64_t)z * p.sDb;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < MT; ++i) {
             int row = m0 + ty * 4 + (i & 3) + (i >> 2) * (BM / 2);
             row = row < p.M ? row : p.M - 1;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < MT; ++j) {
                 int col = n0 + tx * 4 + (j & 3) + (j >> 2) * (BN / 2);
                 col = col < p.N ? col : p.N - 1;
                 dm[i][j] = iadd(kMant & f2i(__ldg(Db + (int64_t)row * p.sDm + (int64_t)col * p.sDn)), p.off);
@@ -340,9 +346,9 @@ gemm_kernel(const GemmParams p) {
 
 #define PAMK_FRAGMENTS(kk)                                                                              \
         const int4 a0 = *reinterpret_cast<const int4*>(as + (kk) * row_stride(BM) + ty * 4);           \
-        const int4 a1 = *reinterpret_cast<const int4*>(as + (kk) * row_stride(BM) + ty * 4 + BM / 2);  \
+        const int4 a1 = MT == 8 ? *reinterpret_cast<const int4*>(as + (kk) * row_stride(BM) + ty * 4 + BM / 2) : a0; \
         const int4 b0 = *reinterpret_cast<const int4*>(bs + (kk) * row_stride(BN) + tx * 4);           \
-        const int4 b1 = *reinterpret_cast<const int4*>(bs + (kk) * row_stride(BN) + tx * 4 + BN / 2);  \
+        const int4 b1 = MT == 8 ? *reinterpret_cast<const int4*>(bs + (kk) * row_stride(BN) + tx * 4 + BN / 2) : b0; \
         const int a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};                              \
         const int b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 
@@ -351,9 +357,9 @@ gemm_kernel(const GemmParams p) {
             for (int kk = 0; kk < BK; ++kk) {
                 PAMK_FRAGMENTS(kk)
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
+                for (int i = 0; i < MT; ++i)
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[i][j] = fadd(acc[i][j], i2f(PAMK_PRODUCT(a[i], b[j])));
+                    for (int j = 0; j < MT; ++j) acc[i][j] = fadd(acc[i][j], i2f(PAMK_PRODUCT(a[i], b[j])));
             }
         } else if (MODE == kPam && path == kFlush) {
             // (deeper unrolling gains 2 % on all-flush inputs and loses 40 % when slabs alternate
@@ -361,13 +367,13 @@ gemm_kernel(const GemmParams p) {
 #pragma unroll 2
             for (int kk = 0; kk < BK; ++kk) {
                 PAMK_FRAGMENTS(kk)
-                float araw[8];          // a[] holds pre-biased patterns; the product needs the values
+                float araw[MT];          // a[] holds pre-biased patterns; the product needs the values
 #pragma unroll
-                for (int i = 0; i < 8; ++i) araw[i] = PAMK_RAW(a[i]);
+                for (int i = 0; i < MT; ++i) araw[i] = PAMK_RAW(a[i]);
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
+                for (int i = 0; i < MT; ++i)
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
+                    for (int j = 0; j < MT; ++j) {
                         const float mag = fabsf(fmul(araw[i], i2f(b[j])));
                         if (mag > i2f(kFlushBits)) acc[i][j] = fadd(acc[i][j], i2f(PAMK_PRODUCT(a[i], b[j])));
                     }
@@ -377,28 +383,28 @@ gemm_kernel(const GemmParams p) {
             for (int kk = 0; kk < BK; ++kk) {
                 PAMK_FRAGMENTS(kk)
                 if constexpr (MODE == kPam) {
-                    float araw[8];
+                    float araw[MT];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) araw[i] = PAMK_RAW(a[i]);
+                    for (int i = 0; i < MT; ++i) araw[i] = PAMK_RAW(a[i]);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
+                    for (int i = 0; i < MT; ++i)
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
+                        for (int j = 0; j < MT; ++j) {
                             const float mag = fabsf(fmul(araw[i], i2f(b[j])));
                             const float prod = mag <= i2f(kPassBits) ? i2f(PAMK_PRODUCT(a[i], b[j])) : quiet_nan();
                             if (!(mag <= i2f(kFlushBits))) acc[i][j] = fadd(acc[i][j], prod);
                         }
                 } else if constexpr (MODE == kStd) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
+                    for (int i = 0; i < MT; ++i)
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[i][j] = __fmaf_rn(i2f(a[i]), i2f(b[j]), acc[i][j]);
+                        for (int j = 0; j < MT; ++j) acc[i][j] = __fmaf_rn(i2f(a[i]), i2f(b[j]), acc[i][j]);
                 } else {
                     // acc += delta * 2^slope, slope from the non-delta operand and D
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
+                    for (int i = 0; i < MT; ++i)
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
+                        for (int j = 0; j < MT; ++j) {
                             const int other = MODE == kBwdL ? b[j] : a[i];
                             const float delta = i2f(MODE == kBwdL ? a[i] : b[j]);
                             acc[i][j] = __fmaf_rn(delta, i2f(kSignExp & iadd(other, dm[i][j])), acc[i][j]);
@@ -415,23 +421,20 @@ gemm_kernel(const GemmParams p) {
     // ---- epilogue ----------------------------------------------------------------------------
     float* Cz = p.C + ((int64_t)sp * p.batch + z) * ((int64_t)p.M * p.N);
     const bool vec_out = (p.N & 3) == 0 && aligned16(p.C);
-    if (p.bias != nullptr && p.splits == 1) {          // (with split-K the reduction pass adds it)
+    const bool add_bias = p.bias != nullptr && p.splits == 1;   // (with split-K the reduction pass adds it)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int col = n0 + tx * 4 + (j & 3) + (j >> 2) * (BN / 2);
-            const float bj = col < p.N ? __ldg(p.bias + col) : 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i][j] = fadd(acc[i][j], bj);
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < MT; ++i) {
         const int row = m0 + ty * 4 + (i & 3) + (i >> 2) * (BM / 2);
         if (row >= p.M) continue;
         float* crow = Cz + (int64_t)row * p.N;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < MT / 4; ++h) {
             const int col = n0 + tx * 4 + h * (BN / 2);
+            if (add_bias) {                            // the bias row is re-read per output row (it stays in L1)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (col + j < p.N) acc[i][h * 4 + j] = fadd(acc[i][h * 4 + j], __ldg(p.bias + col + j));
+            }
             if (vec_out) {
                 if (col < p.N)
                     *reinterpret_cast<float4*>(crow + col) =
@@ -482,8 +485,10 @@ bool vectorisable(const MatArg& m, bool kc, int rows, int K) {
 // ---- planning: tile shape and split-K ---------------------------------------------------------------
 // The kernel is issue-bound, so the time of a launch is (the largest number of tiles any SM ends up
 // with) x (work per tile), inflated when an SM holds too few warps to keep its schedulers busy.
+enum TileKind { kTileLarge = 0, kTileSmall = 1, kTileTiny = 2 };
+
 struct Plan {
-    bool small;      // 64x64 tiles instead of 128x128
+    int tile;        // TileKind
     int splits;
     double cost;
 };
@@ -508,14 +513,15 @@ Plan plan_for(int mode, int64_t batch, int64_t M, int64_t N, int64_t K, int spli
         // measured: 16 resident warps per SM saturate the issue slots, 14 reach about 86 % of that,
         // 8 about 74 %
         const double util = warps >= 16.0 ? 1.0 : (warps >= 8.0 ? 0.58 + 0.02 * warps : warps / 10.8);
-        const double staging = T::BM >= 128 ? 1.0 : 1.06;    // the small tile stages twice the bytes per MAC
+        // the smaller the tile, the more bytes are staged (and fragments loaded) per MAC
+        const double staging = T::BM >= 128 ? 1.0 : (T::BM >= 64 ? 1.06 : 1.25);
         // every CTA also pays a prologue (first loads exposed) and an epilogue worth about 16 k-steps
         const double per_cta = (double)(chunk_slabs * T::BK) + 16.0;
         return (double)per_sm * T::BM * T::BN * per_cta / util * staging +
                (s > 1 ? 1.1e6 : 0.0);                         // the reduction pass and its launch (~12 us)
     };
     Plan pl;
-    pl.small = T::BM < 128;
+    pl.tile = T::BM >= 128 ? kTileLarge : (T::BM >= 64 ? kTileSmall : kTileTiny);
     int64_t s = split_request > 0 ? split_request : 1, actual = 1;
     pl.cost = cost_of(s, &actual);
     pl.splits = (int)actual;
@@ -538,15 +544,23 @@ Plan plan_for(int mode, int64_t batch, int64_t M, int64_t N, int64_t K, int spli
     return pl;
 }
 
-// 0: choose by cost; 1: always the large tile; 2: the small tile wherever it exists.
+// 0: choose by cost; 1: always the large tile; 2: the 64x64 tile wherever it exists; 3: the 32x32
+// tile wherever it exists (PAM products), else the 64x64 tile.
 int g_tile_policy = 0;
 
 Plan make_plan(int mode, int64_t batch, int64_t M, int64_t N, int64_t K, int split_request) {
     const Plan large = plan_for<TileLarge>(mode, batch, M, N, K, split_request);
     if (mode == kStd || g_tile_policy == 1) return large;    // the true-multiply product uses the large tile
     const Plan small = plan_for<TileSmall>(mode, batch, M, N, K, split_request);
-    if (g_tile_policy == 2) return small;
-    return small.cost < large.cost ? small : large;
+    if (g_tile_policy == 2 || (g_tile_policy == 3 && mode != kPam)) return small;
+    Plan best = small.cost < large.cost ? small : large;
+    if (mode == kPam && (g_tile_policy == 3 || M <= TileTiny::BM || N <= TileTiny::BN)) {
+        // only where at least half of every 64x64 tile would be empty: per product the 32x32 tile
+        // is slower than the cost model's occupancy term suggests
+        const Plan tiny = plan_for<TileTiny>(mode, batch, M, N, K, split_request);
+        if (g_tile_policy == 3 || tiny.cost < 0.9 * best.cost) best = tiny;
+    }
+    return best;
 }
 
 bool workspace_ok(const void* ws, size_t bytes, int splits, int64_t count) {
@@ -563,13 +577,14 @@ int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspa
         return e == cudaSuccess ? PAMK_OK : record_cuda_error(e);
     }
     if (split_k < 0) return PAMK_ERR_ARG;
-    Plan pl = p.K == 0 ? Plan{true, 1, 0.0} : make_plan(mode, p.batch, p.M, p.N, p.K, split_k);   // K = 0: rows of bias
+    Plan pl = p.K == 0 ? Plan{kTileSmall, 1, 0.0} : make_plan(mode, p.batch, p.M, p.N, p.K, split_k);   // K = 0: rows of bias
     if (pl.splits > 1 && !workspace_ok(workspace, workspace_bytes, pl.splits, count)) {
         if (split_k != 0) return PAMK_ERR_WORKSPACE;         // an explicit split needs its scratch
         pl = make_plan(mode, p.batch, p.M, p.N, p.K, 1);     // automatic: fall back to no split
     }
-    const int bm = pl.small ? TileSmall::BM : TileLarge::BM, bn = pl.small ? TileSmall::BN : TileLarge::BN;
-    const int bk = pl.small ? TileSmall::BK : TileLarge::BK;
+    const int bm = pl.tile == kTileTiny ? TileTiny::BM : (pl.tile == kTileSmall ? TileSmall::BM : TileLarge::BM);
+    const int bn = pl.tile == kTileTiny ? TileTiny::BN : (pl.tile == kTileSmall ? TileSmall::BN : TileLarge::BN);
+    const int bk = pl.tile == kTileTiny ? TileTiny::BK : (pl.tile == kTileSmall ? TileSmall::BK : TileLarge::BK);
     float* out = p.C;
     if (pl.splits > 1) p.C = static_cast<float*>(workspace);
     const int slabs_total = (p.K + bk - 1) / bk;
@@ -583,17 +598,18 @@ int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspa
     int rc;
     switch (mode) {
         case kPam:
-            rc = pl.small ? dispatch<kPam, TileSmall>(p, a_kc, b_kc, vec, grid, st)
-                          : dispatch<kPam, TileLarge>(p, a_kc, b_kc, vec, grid, st);
+            rc = pl.tile == kTileTiny    ? dispatch<kPam, TileTiny>(p, a_kc, b_kc, vec, grid, st)
+                 : pl.tile == kTileSmall ? dispatch<kPam, TileSmall>(p, a_kc, b_kc, vec, grid, st)
+                                         : dispatch<kPam, TileLarge>(p, a_kc, b_kc, vec, grid, st);
             break;
         case kStd: rc = dispatch<kStd, TileLarge>(p, a_kc, b_kc, vec, grid, st); break;
         case kBwdL:
-            rc = pl.small ? dispatch<kBwdL, TileSmall>(p, a_kc, b_kc, vec, grid, st)
-                          : dispatch<kBwdL, TileLarge>(p, a_kc, b_kc, vec, grid, st);
+            rc = pl.tile == kTileSmall ? dispatch<kBwdL, TileSmall>(p, a_kc, b_kc, vec, grid, st)
+                                       : dispatch<kBwdL, TileLarge>(p, a_kc, b_kc, vec, grid, st);
             break;
         default:
-            rc = pl.small ? dispatch<kBwdR, TileSmall>(p, a_kc, b_kc, vec, grid, st)
-                          : dispatch<kBwdR, TileLarge>(p, a_kc, b_kc, vec, grid, st);
+            rc = pl.tile == kTileSmall ? dispatch<kBwdR, TileSmall>(p, a_kc, b_kc, vec, grid, st)
+                                       : dispatch<kBwdR, TileLarge>(p, a_kc, b_kc, vec, grid, st);
             break;
     }
     if (rc != PAMK_OK || pl.splits == 1) return rc;
@@ -656,7 +672,7 @@ size_t pamk_matmul_workspace_bytes(int64_t batch, int64_t M, int64_t N, int spli
 }
 
 int pamk_matmul_set_tile_policy(int policy) {
-    if (policy < 0 || policy > 2) return PAMK_ERR_ARG;
+    if (policy < 0 || policy > 3) return PAMK_ERR_ARG;
     g_tile_policy = policy;
     return PAMK_OK;
 }

@@ -41,7 +41,7 @@ def K(oracle):
     return oracle.kernels()
 
 
-@pytest.fixture(params=[1, 2], ids=["tile128", "tile64"])
+@pytest.fixture(params=[1, 2, 3], ids=["tile128", "tile64", "tile32"])
 def tile(request, pam):
     """Runs a matrix-product test once per CTA tile shape (the library picks one per problem)."""
     from pam_b200 import _lib
