@@ -31,6 +31,11 @@ MACS_PER_STEP = 3 * TOKENS * sum(k * n for k, n in LAYERS)
 METRIC = "PAM-GEMM MAC/s (fp32), DeiT-tiny linear-layer set fwd+bwd(approx) + pam_ln"
 
 
+# mean DRAM traffic of one PAM GEMM launch of the 192->576 layer, from the ncu capture summarised in
+# profiles/gemm_pam_tile64_deit_shapes_ncu.md (operands mostly stay in the 126 MB L2)
+GEMM_DRAM_BYTES_PER_LAUNCH = (10.2e6 + 36.0e6 + 333.5e6) / 3
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -311,7 +316,11 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
             "roofline": {"bound": "issue (INT32 add + FP32 add per MAC)", "achieved": gemm_rate / 1e12, "peak": mac_peak / 1e12,
-                         "unit": "T PAM-MAC/s", "frac": gemm_rate / mac_peak, "traffic": None,
+                         "unit": "T PAM-MAC/s", "frac": gemm_rate / mac_peak, "traffic": GEMM_DRAM_BYTES_PER_LAUNCH,
+                         "traffic_note": "DRAM bytes per GEMM launch, mean of the three captured launches of the 192->576 layer "
+                                         "(ncu dram__bytes_read.sum + dram__bytes_write.sum: 10 MB forward, 36 MB input gradient, "
+                                         "333 MB weight gradient incl. its 43 split-K partials); algorithmic 40 MB; irrelevant to an "
+                                         "issue-bound kernel (about 1 % of HBM bandwidth)",
                          "kernel": "gemm_kernel<pam> (12 launches of the step, timed alone)",
                          "peak_source": "measured live: 1:1 INT32-add/FP32-add register chains (pamk_issue_rate)",
                          "issue_rates_T_per_s": {k: v / 1e12 for k, v in peak.items()}},
