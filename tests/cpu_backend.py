@@ -75,6 +75,20 @@ class FakeLib:
         self.o.orc_matmul(A, B, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, kind, pam_oracle.offset_to_int(offset))
         return 0
 
+    def pamk_matmul_bias(self, kind, A, B, bias, C, batch, M, N, K, *rest):
+        status = self.pamk_matmul(kind, A, B, C, batch, M, N, K, *rest)
+        if status == 0 and bias and batch * M * N:
+            out = _view(C, batch * M * N).reshape(batch * M, N)
+            out += _view(bias, N)                       # one fp32 add per element, after the sum
+        return status
+
+    def pamk_column_sum_workspace_bytes(self, rows, cols): return 0
+
+    def pamk_column_sum(self, X, out, rows, cols, ws, wsb, s):
+        # torch's CPU sum, so that host-layer results keep the reference's own reduction
+        _view(out, cols)[:] = torch.from_numpy(_view(X, rows * cols).reshape(rows, cols)).sum(0).numpy() if rows else 0.0
+        return 0
+
     def pamk_matmul_bwd(self, L, R, D, C, batch, M, N, K, *rest):
         strides, (delta_l, offset, _split, _ws, _wsb, _s) = rest[:9], rest[9:]
         self.calls.append(("matmul_bwd", (batch, M, N, K), strides, delta_l))

@@ -126,3 +126,23 @@ def test_patch_convolution_without_unfold_equals_unfold_route(backend):
         outs.append((y.detach(), x.grad, w.grad, bias.grad))
     for name, got, want in zip(("y", "dx", "dw", "db"), *outs):
         assert torch.equal(got, want), name
+
+
+@pytest.mark.parametrize("approx", [True, False])
+def test_linear_with_bias_in_the_epilogue_equals_product_plus_add(backend, approx):
+    """The autograd function behind the fused `linear` (bias added by the product's epilogue, bias
+    gradient by the column-sum entry point) against the reference's composition, product then add."""
+    from pam_b200 import cuda_bindings as cb
+    g = torch.Generator().manual_seed(21)
+    X, W, b, gy = (torch.randn(9, 14, generator=g), torch.randn(6, 14, generator=g), torch.randn(6, generator=g),
+                   torch.randn(9, 6, generator=g))
+    outs = []
+    for route in (lambda x, w, bias: cb.pam_linear(x, w, bias, approx_bwd=approx),
+                  lambda x, w, bias: pam.matmul(x, w.T, approx_bwd=approx) + bias):
+        x, w, bias = (t.clone().requires_grad_() for t in (X, W, b))
+        y = route(x, w, bias)
+        y.backward(gy)
+        outs.append((y.detach(), x.grad, w.grad, bias.grad))
+    for name, got, want in zip(("y", "dx", "dw", "db"), *outs):
+        assert torch.equal(got, want), name
+    assert any(c[0] == "matmul" for c in backend.calls)
