@@ -422,6 +422,17 @@ gemm_kernel(const GemmParams p) {
     float* Cz = p.C + ((int64_t)sp * p.batch + z) * ((int64_t)p.M * p.N);
     const bool vec_out = (p.N & 3) == 0 && aligned16(p.C);
     const bool add_bias = p.bias != nullptr && p.splits == 1;   // (with split-K the reduction pass adds it)
+    if constexpr (MODE != kPam) {
+        // The reference walks K in zero-filled tiles of 32 (cuda_kernels.cu:526-571, 608-629): when K
+        // is not a multiple of 32 it also adds products of zeros, which turns a sum of -0 into +0.
+        // (A PAM sum is never -0: flushed products are +0.)
+        if (p.K & 31) {
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int j = 0; j < MT; ++j) acc[i][j] = fadd(acc[i][j], 0.0f);
+        }
+    }
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
         const int row = m0 + ty * 4 + (i & 3) + (i >> 2) * (BM / 2);
