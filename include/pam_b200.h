@@ -119,11 +119,6 @@ int pamk_matmul_bias(int mul_kind, const float* A, const float* B, const float* 
 size_t pamk_matmul_workspace_bytes(int64_t batch, int64_t M, int64_t N, int split_k);
 /* The split the library would choose for split_k = 0 given unlimited workspace. */
 int pamk_matmul_auto_split(int64_t batch, int64_t M, int64_t N, int64_t K);
-/* Tuning / testing knob (process-wide, not thread-safe): the PAM product picks a 128x128, a 64x64
- * or (for batched products of very small matrices) a 32x32 CTA tile per problem; 0 = by cost model
- * (default), 1 = always 128x128, 2 = always 64x64, 3 = always 32x32 (products that have no 32x32
- * kernel use 64x64).  Results do not depend on the tile. */
-int pamk_matmul_set_tile_policy(int policy);
 
 /* Split-K PAM product for callers that cannot allocate.  It has no counterpart in the reference.
  *

@@ -426,11 +426,17 @@ gemm_kernel(const GemmParams p) {
         // The reference walks K in zero-filled tiles of 32 (cuda_kernels.cu:526-571, 608-629): when K
         // is not a multiple of 32 it also adds products of zeros, which turns a sum of -0 into +0.
         // (A PAM sum is never -0: flushed products are +0.)
+        // In the exact-gradient kernel a padded term is pam_bwd(D, 0, 0) = 0 * slope(D, 0)
+        // (cuda_kernels.cu:49-57, 795-809): with an offset below one and a small mantissa of D the
+        // slope's bit pattern is -inf and the term is NaN.
         if (p.K & 31) {
 #pragma unroll
             for (int i = 0; i < MT; ++i)
 #pragma unroll
-                for (int j = 0; j < MT; ++j) acc[i][j] = fadd(acc[i][j], 0.0f);
+                for (int j = 0; j < MT; ++j) {
+                    if constexpr (MODE == kStd) acc[i][j] = fadd(acc[i][j], 0.0f);
+                    else acc[i][j] = __fmaf_rn(0.0f, i2f(kSignExp & dm[i][j]), acc[i][j]);
+                }
         }
     }
 #pragma unroll
@@ -682,7 +688,7 @@ size_t pamk_matmul_workspace_bytes(int64_t batch, int64_t M, int64_t N, int spli
     return (size_t)split_k * (size_t)batch * (size_t)M * (size_t)N * sizeof(float);
 }
 
-int pamk_matmul_set_tile_policy(int policy) {
+int pamk_test_set_tile_policy(int policy) {
     if (policy < 0 || policy > 3) return PAMK_ERR_ARG;
     g_tile_policy = policy;
     return PAMK_OK;

@@ -1,4 +1,4 @@
-"""The C-ABI library builds, loads and exports every symbol that include/pam_b200.h declares
+"""The C-ABI library builds, loads and exports every symbol that the headers under include/ declare
 (no kernel is launched here)."""
 import ctypes
 import re
@@ -7,7 +7,7 @@ from conftest import ROOT
 
 
 def _declared():
-    text = (ROOT / "include" / "pam_b200.h").read_text()
+    text = "".join(p.read_text() for p in sorted((ROOT / "include").glob("*.h")))
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(pamk_\w+)\s*\(", text)))
 

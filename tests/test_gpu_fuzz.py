@@ -50,7 +50,7 @@ def test_random_product_against_oracle(oracle, case):
     bias = torch.randn(N, generator=g) if mode == "pam" and rnd.random() < 0.4 else None
 
     lib = _lib.lib()
-    _lib.check(lib.pamk_matmul_set_tile_policy(tile), "tile policy")
+    _lib.check(lib.pamk_test_set_tile_policy(tile), "tile policy")
     try:
         if mode in ("pam", "std"):
             kind = 0 if mode == "pam" else 1
@@ -65,7 +65,7 @@ def test_random_product_against_oracle(oracle, case):
             want = K.pam_matmul_bwd(A, B, D, True, True, mode == "bwd_l", offset)
             terms = K.pam_matmul_bwd(A.abs(), B.abs(), D.abs(), True, True, mode == "bwd_l", offset)
     finally:
-        lib.pamk_matmul_set_tile_policy(0)
+        lib.pamk_test_set_tile_policy(0)
 
     what = f"case {case}: {mode} {batch}x{M}x{N}x{Kdim} tile={tile} split={split} bias={bias is not None}"
     if split == 1:

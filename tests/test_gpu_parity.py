@@ -45,9 +45,9 @@ def K(oracle):
 def tile(request, pam):
     """Runs a matrix-product test once per CTA tile shape (the library picks one per problem)."""
     from pam_b200 import _lib
-    _lib.check(_lib.lib().pamk_matmul_set_tile_policy(request.param), "tile policy")
+    _lib.check(_lib.lib().pamk_test_set_tile_policy(request.param), "tile policy")
     yield request.param
-    _lib.lib().pamk_matmul_set_tile_policy(0)
+    _lib.lib().pamk_test_set_tile_policy(0)
 
 
 SPECIALS = [0.0, -0.0, 1e-40, -1e-40, 1.4e-45, -1.4e-45, 1e30, -1e30, 1e-30, -1e-30]
