@@ -1,21 +1,26 @@
 """Benchmark of the PAM hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--size n]
 
-Workload (one "step"): the DeiT-tiny PAM linear-layer set — activations X[12608 x 192] (batch 64 x
-197 tokens) N(0,1), trunc-normal(0.02) weights, the four GEMMs 192->576, 192->192, 192->768,
-768->192 forward and backward with approx_bwd (12 PAM GEMMs, 16.73 G PAM multiply-accumulates),
-plus pam_ln (LayerNorm) over the 192-wide rows forward and backward.  Synthetic seeded data.
+Headline workload (one "step"): the largest square product of the scaling sweep — one PAM matrix
+product C = A (x) B with M = N = K = 16384 in fp32, entries N(0,1) with 1 % injected special values
+(zeros of both signs, denormals, magnitudes 1e30 and 1e-30) generated on the device from a seed.
+With N > 1 ranks (torchrun) the rows of A are sharded: every rank holds its own 16384-row block of
+a [N*16384 x 16384] A and the whole B (weak scaling, no collective on the data path); the time is the
+max over ranks.
 
-Prints ONE JSON line: PAM-GEMM MAC/s (GEMM multiply-accumulates of the step / step time, the
-LayerNorm included in the time), with the issue-rate roofline of the dominant kernel, the
-end-to-end figure with host buffers, clocks sampled during the timed region and the CPU baseline.
-With N > 1 (torchrun) every rank runs the same per-GPU workload on its own rows (weak scaling,
-no collective on the data path); the time is the max over ranks.
+Prints ONE JSON line: PAM-GEMM MAC/s, the issue-rate roofline of the product kernel on this input,
+the end-to-end figure with host buffers, clocks sampled during the timed region, per-rank times, and
+secondary objects measured in the same run: the same product without special values, the DeiT-tiny
+linear-layer set, the HBM-bound kernels (mul / div / pam_ln) against the measured copy bandwidth,
+the reference's own CUDA kernel on the same inputs (when its build is present), the two training
+steps, and the reference's CPU implementation on a bounded sample.
 """
 import argparse
+import ctypes
 import json
 import os
+import pathlib
 import statistics
 import subprocess
 import sys
@@ -24,16 +29,22 @@ import time
 
 import torch
 
+ROOT = pathlib.Path(__file__).resolve().parent
+
+# the DeiT-tiny linear-layer set (secondary workload)
 LAYERS = ((192, 576), (192, 192), (192, 768), (768, 192))
 TOKENS = 12608
 LN_WIDTH = 192
-MACS_PER_STEP = 3 * TOKENS * sum(k * n for k, n in LAYERS)
-METRIC = "PAM-GEMM MAC/s (fp32), DeiT-tiny linear-layer set fwd+bwd(approx) + pam_ln"
+LAYER_SET_MACS = 3 * TOKENS * sum(k * n for k, n in LAYERS)
 
+SPECIALS = [0.0, -0.0, 1e-40, -1e-40, 1.4e-45, -1.4e-45, 1e30, -1e30, 1e-30, -1e-30]
+METRIC = "PAM-GEMM MAC/s (fp32)"
+SM_LANES = 128          # fp32 / int32 lanes per SM: one INT32 add + one FP32 add per MAC -> lanes * clock / 2
 
-# mean DRAM traffic of one PAM GEMM launch of the 192->576 layer, from the ncu capture summarised in
-# profiles/gemm_pam_tile64_deit_shapes_ncu.md (operands mostly stay in the 126 MB L2)
-GEMM_DRAM_BYTES_PER_LAUNCH = (10.2e6 + 36.0e6 + 333.5e6) / 3
+# DRAM bytes (ncu dram__bytes_read.sum + dram__bytes_write.sum) of one product launch of the
+# headline kernel on an 8192^3 input with 1 % specials; a 16384^3 launch streams each operand from
+# DRAM once per wave of output tiles, so its traffic is scaled by the number of multiply-accumulates.
+GEMM_DRAM_BYTES_8192 = None
 
 
 def parse():
@@ -42,21 +53,36 @@ def parse():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cpu-rows", type=int, default=0, help="rows of X in the CPU sample (0 = auto)")
+    ap.add_argument("--size", type=int, default=None,
+                    help="edge of the headline product (default 16384); with --case: GEMM edge or log2 of the element count")
+    ap.add_argument("--cpu-rows", type=int, default=0, help="rows of A in the CPU sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="headline only (for profilers)")
     ap.add_argument("--case", default=None,
                     help="run one kernel in isolation (for profiling) instead of the benchmark: "
-                         "gemm | gemm_specials | deit_gemms | deit_gemms_exact | mul | layer_norm_fwd | layer_norm_bwd | "
-                         "softmax_fwd | softmax_bwd | adam | column_sum; or a full training step, also under torchrun "
-                         "with --gpus N: deit_step | transformer_step")
-    ap.add_argument("--size", type=int, default=4096, help="--case size: GEMM edge, or log2 of the element count")
+                         "gemm | gemm_specials | gemm_relu | deit_gemms | deit_gemms_exact | attention_gemms | mul | div | "
+                         "layer_norm_fwd | layer_norm_bwd | softmax_fwd | softmax_bwd | adam | column_sum; or a full training "
+                         "step, also under torchrun with --gpus N: deit_step | transformer_step")
     ap.add_argument("--reps", type=int, default=2)
     ap.add_argument("--exact-bwd", action="store_true",
                     help="training-step cases: exact piecewise-affine gradients (approx_bwd=False) instead of approx_bwd=True")
     return ap.parse_args()
 
 
-def make_inputs(seed, device=None, pin=False):
+def randn_with_specials(shape, seed, dev, frac=0.01, values=SPECIALS):
+    """N(0,1) entries with a fraction overwritten by a cycle of special values (seeded, on `dev`)."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    t = torch.randn(shape, generator=g, device=dev)
+    if frac > 0:
+        flat = t.view(-1)
+        count = max(1, int(flat.numel() * frac))
+        idx = torch.randint(0, flat.numel(), (count,), generator=g, device=dev)
+        vals = torch.tensor(values, dtype=torch.float32, device=dev)
+        flat[idx] = vals[torch.arange(count, device=dev) % vals.numel()]
+    return t
+
+
+def layer_set_inputs(seed, device=None):
     g = torch.Generator().manual_seed(seed)
     data = {"X": [], "W": [], "G": []}
     for k, n in LAYERS:
@@ -65,18 +91,23 @@ def make_inputs(seed, device=None, pin=False):
         data["G"].append(torch.randn(TOKENS, n, generator=g))
     data["LNX"] = torch.randn(TOKENS, LN_WIDTH, generator=g)
     data["LNG"] = torch.randn(TOKENS, LN_WIDTH, generator=g)
-
-    def place(t):
-        if device is not None:
-            return t.to(device)
-        return t.pin_memory() if pin else t
+    place = (lambda t: t.to(device)) if device is not None else (lambda t: t)
     return {k: [place(t) for t in v] if isinstance(v, list) else place(v) for k, v in data.items()}
+
+
+def hbm_peak():
+    """Measured copy bandwidth of this pool's B200s (GB/s) and where the figure comes from."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    except (OSError, ValueError, KeyError):
+        return 6650.0, "fallback (earlier measurement on this pool)"
 
 
 # ---- clocks ---------------------------------------------------------------------------------------
 
 class ClockSampler:
-    """Samples nvidia-smi for one GPU every 20 ms while the device-timed regions run."""
+    """Samples nvidia-smi for one GPU every 50 ms while the device-timed regions run."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
@@ -88,7 +119,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -101,17 +132,18 @@ class ClockSampler:
 
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.25)
+            time.sleep(0.15)
             self.proc.terminate()
             self.thread.join(timeout=2)
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
+        sm, mx, power, reasons = [], [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for r in self.rows:
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
+                power.append(float(r[2]))
             except (ValueError, IndexError):
                 continue
             for name, val in zip(names, r[3:7]):
@@ -119,7 +151,38 @@ class ClockSampler:
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": statistics.median(sm), "sm_min_mhz": min(sm), "sm_max_mhz": max(mx), "power_w_max": max(power),
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def timed(fn, reps, flush=None):
+    """Mean CUDA-event milliseconds of `fn` over `reps` calls (one warm-up call first)."""
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total = 0.0
+    for _ in range(reps):
+        if flush is not None:
+            flush.zero_()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / reps
+
+
+def issue_rates(lib, dev):
+    """Live INT32/FP32 issue rates from register-only chains (instructions-pairs per second)."""
+    from pam_b200 import _lib
+    peak = {}
+    scratch = torch.zeros(4, dtype=torch.int32, device=dev)
+    for name, variant in (("fadd", 0), ("iadd", 1), ("iadd_fadd", 2), ("imad_fadd", 3), ("mixed_fadd", 4)):
+        ms, steps_done = ctypes.c_float(), ctypes.c_double()
+        _lib.check(lib.pamk_issue_rate(variant, 8000, 4, scratch.data_ptr(), ctypes.byref(ms), ctypes.byref(steps_done),
+                                       torch.cuda.current_stream().cuda_stream), "issue_rate")
+        peak[name] = steps_done.value / (ms.value * 1e-3)
+    return peak
 
 
 # ---- our arm ------------------------------------------------------------------------------------------
@@ -134,35 +197,26 @@ def run_ours(args):
         raise SystemExit("timing rules need --warmup >= 3")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    dist = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
     import pam_b200 as pam
-    from pam_b200 import _lib
+    from pam_b200 import _lib, parallel
     torch.backends.cuda.matmul.allow_tf32 = False
     lib = _lib.lib()                       # fails loudly if the CUDA library is missing
+    n = args.size or 16384
+    macs = float(n) ** 3
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
 
-    d = make_inputs(1234 + rank, device=dev)
-    ln = pam.LayerNorm(LN_WIDTH, eps=1e-6, approx_bwd=True).to(dev)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # > 126 MB L2
+    # rank r's block of rows of A (seed + rank) and the shared B
+    A = randn_with_specials((n, n), 4000 + rank, dev)
+    B = randn_with_specials((n, n), 3999, dev)
 
-    def step(data, keep=False):
-        outs = []
-        for X, W, G in zip(data["X"], data["W"], data["G"]):
-            X = X.detach().requires_grad_()
-            W = W.detach().requires_grad_()
-            Y = pam.linear(X, W, approx_bwd=True)
-            Y.backward(G)
-            if keep:
-                outs += [Y.detach(), X.grad, W.grad]
-        x = data["LNX"].detach().requires_grad_()
-        y = ln(x)
-        y.backward(data["LNG"])
-        ln.weight.grad = ln.bias.grad = None
-        if keep:
-            outs += [y.detach(), x.grad]
-        return outs
+    def step():
+        with torch.no_grad():
+            return pam.matmul(A, B)
 
     def barrier():
         torch.cuda.synchronize()
@@ -171,164 +225,210 @@ def run_ours(args):
             torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        step(d)
+        step()
     barrier()
 
-    # ---- value: inputs resident in HBM, per-step CUDA events, L2 flushed between steps ----------
+    # ---- value: inputs resident in HBM; operands (1 GiB each at the default size) exceed the L2 ----
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     launches0 = lib.pamk_launch_count()
     clocks = ClockSampler(local)
     clocks.__enter__()
     barrier()
+    region0, region1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    region0.record()
+    enqueue_s = 0.0
     for e0, e1 in ev:
-        flush.zero_()
+        t0 = time.perf_counter()
         e0.record()
-        step(d)
+        step()
         e1.record()
+        enqueue_s += time.perf_counter() - t0
+    region1.record()
     barrier()
-    launches = lib.pamk_launch_count() - launches0
-    total_ms = sum(e0.elapsed_time(e1) for e0, e1 in ev)
-
-    # ---- roofline of the dominant kernel: the 12 GEMM launches alone -------------------------------
-    def gemms_only():
-        ck = pam.cuda_bindings
-        for X, W, G in zip(d["X"], d["W"], d["G"]):
-            ck._matmul(0, X, W.T, 1.0, 2)
-            ck._matmul(0, G, W, 1.0, 2)
-            ck._matmul(0, X.T, G, 1.0, 2)
-    for _ in range(3):
-        gemms_only()
-    torch.cuda.synchronize()
-    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = max(3, args.steps // 2)
-    gemm_ms = 0.0
-    for _ in range(reps):
-        flush.zero_()
-        g0.record()
-        gemms_only()
-        g1.record()
-        torch.cuda.synchronize()
-        gemm_ms += g0.elapsed_time(g1)
-    gemm_rate = MACS_PER_STEP * reps / (gemm_ms * 1e-3)
-
-    import ctypes
-    peak = {}
-    scratch = torch.zeros(4, dtype=torch.int32, device=dev)
-    for name, variant in (("fadd", 0), ("iadd", 1), ("iadd_fadd", 2), ("imad_fadd", 3), ("mixed_fadd", 4)):
-        ms, steps_done = ctypes.c_float(), ctypes.c_double()
-        _lib.check(lib.pamk_issue_rate(variant, 8000, 4, scratch.data_ptr(), ctypes.byref(ms), ctypes.byref(steps_done),
-                                       torch.cuda.current_stream().cuda_stream), "issue_rate")
-        peak[name] = steps_done.value / (ms.value * 1e-3)
-    mac_peak = max(peak["iadd_fadd"], peak["imad_fadd"], peak["mixed_fadd"])
     clocks.__exit__(None, None, None)
+    launches = lib.pamk_launch_count() - launches0
+    kernel_ms = sum(e0.elapsed_time(e1) for e0, e1 in ev)
+    region_ms = region0.elapsed_time(region1)
+    clk = clocks.summary()
 
-    # ---- e2e: host buffers in, results out, through the public API ------------------------------------
-    # Copies are pipelined against the compute on two extra streams (PCIe is full duplex): inputs
-    # upload and results download while other layers compute.
-    host = make_inputs(1234 + rank, pin=True)
-    h2d = sum(t.numel() * 4 for v in host.values() for t in (v if isinstance(v, list) else [v]))
-    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    main = torch.cuda.current_stream(dev)
-    out_host = {}
+    peak_chains = issue_rates(lib, dev)
+    live_peak = max(peak_chains["iadd_fadd"], peak_chains["imad_fadd"], peak_chains["mixed_fadd"])
+    clock_peak = 0.98 * sms * SM_LANES * (clk["sm_mhz"] or 0.0) * 1e6 / 2
+    mac_peak = max(live_peak, clock_peak)
 
-    def download(key, tensors):
-        ready = torch.cuda.Event()
-        ready.record(main)
-        s_out.wait_event(ready)
-        with torch.cuda.stream(s_out):
-            for j, t in enumerate(tensors):
-                slot = out_host.get((key, j))
-                if slot is None:
-                    slot = out_host[(key, j)] = torch.empty(t.shape, dtype=t.dtype).pin_memory()
-                slot.copy_(t, non_blocking=True)
-                t.record_stream(s_out)
+    secondary = {}
+    if not args.no_secondary:
+        secondary = run_secondary(args, pam, lib, dev, A, B, n, mac_peak, rank)
+
+    # ---- e2e: host buffers in, result out, through the public API ---------------------------------------
+    e2e_steps = max(3, min(args.steps, 5))
+    hA, hB = A.cpu().pin_memory(), B.cpu().pin_memory()
+    hC = torch.empty(n, n, dtype=torch.float32).pin_memory()
 
     def e2e_step():
-        uploads = []
-        with torch.cuda.stream(s_in):
-            for i in range(len(LAYERS)):
-                trio = [host[k][i].to(dev, non_blocking=True) for k in ("X", "W", "G")]
-                ev = torch.cuda.Event()
-                ev.record(s_in)
-                uploads.append((trio, ev))
-            ln_in = [host["LNX"].to(dev, non_blocking=True), host["LNG"].to(dev, non_blocking=True)]
-            ln_ev = torch.cuda.Event()
-            ln_ev.record(s_in)
-        for i, ((X, W, G), ev) in enumerate(uploads):
-            main.wait_event(ev)
-            for t in (X, W, G):
-                t.record_stream(main)
-            X.requires_grad_()
-            W.requires_grad_()
-            Y = pam.linear(X, W, approx_bwd=True)
-            Y.backward(G)
-            download(i, [Y.detach(), X.grad, W.grad])
-        main.wait_event(ln_ev)
-        x = ln_in[0].requires_grad_()
-        for t in ln_in:
-            t.record_stream(main)
-        y = ln(x)
-        y.backward(ln_in[1])
-        ln.weight.grad = ln.bias.grad = None
-        download("ln", [y.detach(), x.grad])
+        dA = hA.to(dev, non_blocking=True)
+        dB = hB.to(dev, non_blocking=True)
+        with torch.no_grad():
+            hC.copy_(pam.matmul(dA, dB), non_blocking=True)
 
-    # The K steps are timed as one region: step i+1's uploads are queued while step i computes and
-    # downloads (the way a prefetching input pipeline feeds a training loop), so the steady state is
-    # whichever of upload, compute and download is slowest; every byte of every step crosses PCIe
-    # inside the region.
-    e2e_steps = max(3, min(args.steps, 10))
-    for _ in range(2):
-        e2e_step()
-    main.wait_stream(s_out)
-    torch.cuda.synchronize()
+    e2e_step()
     barrier()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     for _ in range(e2e_steps):
         e2e_step()
-    main.wait_stream(s_out)
     t1.record()
     torch.cuda.synchronize()
     e2e_ms = t0.elapsed_time(t1)
-    d2h = sum(t.numel() * 4 for t in out_host.values())
+    del hA, hB, hC
 
-    from pam_b200 import parallel
-    total_ms, e2e_ms = (parallel.max_over_ranks(v, dev) for v in (total_ms, e2e_ms))
+    per_rank = [[round(region_ms / args.steps, 4), round(kernel_ms / args.steps, 4), round(1e3 * enqueue_s / args.steps, 4)]]
+    if world > 1:
+        gathered = [torch.zeros(3, dtype=torch.float64, device=dev) for _ in range(world)]
+        dist.all_gather(gathered, torch.tensor([region_ms / args.steps, kernel_ms / args.steps, 1e3 * enqueue_s / args.steps],
+                                               dtype=torch.float64, device=dev))
+        per_rank = [[round(float(v), 4) for v in g.tolist()] for g in gathered]
+    region_ms, e2e_ms = (parallel.max_over_ranks(v, dev) for v in (region_ms, e2e_ms))
+
+    train = None
+    if not args.no_secondary:
+        train = {name: training_step(args, name, rank, world, dev, steps=5, warmup=3) for name in ("deit_step", "transformer_step")}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_sample(args, target_seconds=12.0)
+        cpu = cpu_sample(args, n, target_seconds=12.0)
 
     if rank == 0:
-        value = world * MACS_PER_STEP * args.steps / (total_ms * 1e-3)
+        value = world * macs * args.steps / (region_ms * 1e-3)
+        kernel_rate = macs * args.steps / (kernel_ms * 1e-3)
         line = {
             "metric": METRIC, "value": value, "unit": "MAC/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "warmup": args.warmup, "ms_per_step": region_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int32 add + fp32 accumulate", "data": "synthetic",
-            "config": {"workload": "configs[1]: DeiT-tiny PAM linear-layer set, X[12608x192], GEMMs 192->576, "
-                                   "192->192, 192->768, 768->192 fwd+bwd approx_bwd, pam_ln over 192-wide rows fwd+bwd",
-                       "macs_per_step_per_gpu": MACS_PER_STEP, "l2": "flushed between timed steps (256 MB write)",
-                       "sharding": "per-GPU replica of the workload on its own rows; no collective"},
-            "e2e": {"value": world * MACS_PER_STEP * e2e_steps / (e2e_ms * 1e-3), "unit": "MAC/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "note": "pinned host inputs -> device -> pam.linear/LayerNorm fwd+bwd -> all outputs and gradients "
-                            "back to pinned host; uploads and downloads overlap the compute on their own streams"},
+            "config": {"workload": f"configs[4]: scaling sweep, square PAM GEMM M=N=K={n}, fp32, N(0,1) inputs with 1% injected "
+                                   "specials (+-0, denormals, +-1e30, +-1e-30), forward product through pam.matmul",
+                       "macs_per_step_per_gpu": macs, "l2": "operands larger than L2 (1 GiB each at 16384)",
+                       "sharding": "rows of A sharded over the ranks (each rank its own n-row block, B replicated); no collective"},
+            "e2e": {"value": world * macs * e2e_steps / (e2e_ms * 1e-3), "unit": "MAC/s",
+                    "h2d_bytes_per_step": 2 * n * n * 4, "d2h_bytes_per_step": n * n * 4,
+                    "note": "pinned host A and B -> device -> pam.matmul -> C back to pinned host, every step"},
             "gpu_launches": int(launches),
-            "clocks": clocks.summary(),
-            "roofline": {"bound": "issue (INT32 add + FP32 add per MAC)", "achieved": gemm_rate / 1e12, "peak": mac_peak / 1e12,
-                         "unit": "T PAM-MAC/s", "frac": gemm_rate / mac_peak, "traffic": GEMM_DRAM_BYTES_PER_LAUNCH,
-                         "traffic_note": "DRAM bytes per GEMM launch, mean of the three captured launches of the 192->576 layer "
-                                         "(ncu dram__bytes_read.sum + dram__bytes_write.sum: 10 MB forward, 36 MB input gradient, "
-                                         "333 MB weight gradient incl. its 43 split-K partials); algorithmic 40 MB; irrelevant to an "
-                                         "issue-bound kernel (about 1 % of HBM bandwidth)",
-                         "kernel": "gemm_kernel<pam> (12 launches of the step, timed alone)",
-                         "peak_source": "measured live: 1:1 INT32-add/FP32-add register chains (pamk_issue_rate)",
-                         "issue_rates_T_per_s": {k: v / 1e12 for k, v in peak.items()}},
+            "clocks": clk,
+            "timed_region_s": region_ms * 1e-3,
+            "macs_per_sm_clock": (kernel_rate / ((clk["sm_mhz"] or float("nan")) * 1e6)),
+            "per_rank": {"columns": ["ms_per_step", "kernel_ms_per_step", "host_enqueue_ms_per_step"], "rows": per_rank},
+            "roofline": {"bound": "issue (INT32 add + FP32 add per MAC)", "achieved": kernel_rate / 1e12, "peak": mac_peak / 1e12,
+                         "unit": "T PAM-MAC/s", "frac": kernel_rate / mac_peak,
+                         "traffic": None if GEMM_DRAM_BYTES_8192 is None else GEMM_DRAM_BYTES_8192 * (n / 8192.0) ** 3,
+                         "kernel": "gemm_kernel<pam, 128x128x16> (one launch per step, rank 0)",
+                         "peak_source": "max(live 1:1 INT32-add/FP32-add register chains, 0.98 * SMs * 128 lanes * median sampled "
+                                        "SM clock / 2)",
+                         "peak_live_chains": live_peak / 1e12, "peak_from_sampled_clock": clock_peak / 1e12,
+                         "peak_nominal_at_max_clock": sms * SM_LANES * (clk["sm_max_mhz"] or 0.0) * 1e6 / 2 / 1e12,
+                         "issue_rates_T_per_s": {k: v / 1e12 for k, v in peak_chains.items()}},
             "cpu_baseline": cpu,
         }
+        line.update(secondary)
+        if train is not None:
+            line["train_steps"] = train
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_secondary(args, pam, lib, dev, A, B, n, mac_peak, rank):
+    """Figures measured beside the headline in the same run (rank-local; rank 0's are printed)."""
+    from pam_b200 import cuda_bindings as cb
+    out = {}
+    macs = float(n) ** 3
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # > 126 MB L2
+
+    # the same product without special values (every slab takes the two-instruction loop)
+    A0, B0 = torch.randn(n, n, device=dev), torch.randn(n, n, device=dev)
+    ms = timed(lambda: cb._matmul(0, A0, B0, 1.0, 2), 3)
+    out["gemm_no_specials"] = {"T_mac_per_s": macs / ms / 1e9, "ms": ms, "frac_of_peak": macs / (ms * 1e-3) / mac_peak}
+    del A0, B0
+
+    # the reference's own CUDA kernel (compiled for sm_100a by baseline/build_ref.py) on the same inputs
+    ref = None
+    try:
+        from baseline import build_ref
+        ref = build_ref.load()
+    except Exception as exc:                                        # noqa: BLE001 (absence is reported, not fatal)
+        out["ref_gpu_kernel"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+    if ref is not None:
+        ours_ms = timed(lambda: cb._matmul(0, A, B, 1.0, 2), 2)
+        ref_ms = timed(lambda: ref.pam_matmul_fwd(A, B, True, True, 1.0), 1)
+        out["ref_gpu_kernel"] = {
+            "what": "pam_matmul_fwd of the reference's pam/cuda_kernels.cu built for sm_100a, same inputs, same run, CUDA events",
+            "headline_gemm": {"ref_ms": ref_ms, "ours_ms": ours_ms, "ref_T_mac_per_s": macs / ref_ms / 1e9,
+                              "speedup_vs_ref_kernel": ref_ms / ours_ms}}
+    elif "ref_gpu_kernel" not in out:
+        out["ref_gpu_kernel"] = {"unavailable": "baseline/_ref/pam_ref_cuda_kernels.so was not built"}
+
+    # the DeiT-tiny linear-layer set: 12 products forward + approx_bwd, pam_ln over the 192-wide rows
+    d = layer_set_inputs(1234 + rank, device=dev)
+    ln = pam.LayerNorm(LN_WIDTH, eps=1e-6, approx_bwd=True).to(dev)
+
+    def layer_set_step():
+        for X, W, G in zip(d["X"], d["W"], d["G"]):
+            X = X.detach().requires_grad_()
+            W = W.detach().requires_grad_()
+            pam.linear(X, W, approx_bwd=True).backward(G)
+        x = d["LNX"].detach().requires_grad_()
+        ln(x).backward(d["LNG"])
+        ln.weight.grad = ln.bias.grad = None
+
+    def layer_set_gemms():
+        for X, W, G in zip(d["X"], d["W"], d["G"]):
+            cb._matmul(0, X, W.T, 1.0, 2)
+            cb._matmul(0, G, W, 1.0, 2)
+            cb._matmul(0, X.T, G, 1.0, 2)
+
+    for _ in range(3):
+        layer_set_step()
+    step_ms = timed(layer_set_step, 10, flush)
+    gemm_ms = timed(layer_set_gemms, 10, flush)
+    out["config2_linear_set"] = {
+        "workload": "configs[1]: DeiT-tiny PAM linear-layer set, X[12608x192], GEMMs 192->576, 192->192, 192->768, 768->192 "
+                    "fwd+bwd approx_bwd, pam_ln over 192-wide rows fwd+bwd; L2 flushed between steps",
+        "T_mac_per_s": LAYER_SET_MACS / step_ms / 1e9, "ms_per_step": step_ms,
+        "gemms_only_T_mac_per_s": LAYER_SET_MACS / gemm_ms / 1e9, "gemms_only_frac_of_peak": LAYER_SET_MACS / (gemm_ms * 1e-3) / mac_peak}
+    if ref is not None:
+        def ref_gemms():
+            for X, W, G in zip(d["X"], d["W"], d["G"]):
+                ref.pam_matmul_fwd(X, W.T, True, False, 1.0)
+                ref.pam_matmul_fwd(G, W, True, True, 1.0)
+                ref.pam_matmul_fwd(X.T, G, False, True, 1.0)
+        ref_ms = timed(ref_gemms, 3, flush)
+        out["ref_gpu_kernel"]["config2_gemms"] = {"ref_ms": ref_ms, "ours_ms": gemm_ms, "speedup_vs_ref_kernel": ref_ms / gemm_ms}
+
+    # HBM-bound kernels: algorithmic bytes / CUDA-event time, against the measured copy bandwidth
+    peak_gbs, peak_src = hbm_peak()
+    hbm = {"peak_GBps": peak_gbs, "peak_source": peak_src, "kernels": {}}
+    for log2n in (26, 28):
+        count = 1 << log2n
+        a = randn_with_specials((count,), 50 + log2n, dev)
+        b = randn_with_specials((count,), 60 + log2n, dev)
+        for name, fn in (("mul", pam.mul), ("div", pam.div)):
+            ms = timed(lambda: fn(a, b), 3)
+            gbs = 12.0 * count / ms / 1e6
+            hbm["kernels"][f"{name}_2^{log2n}"] = {"GBps": gbs, "frac": gbs / peak_gbs, "bytes_per_element": 12}
+        del a, b
+        rows = count // LN_WIDTH
+        x = randn_with_specials((rows, LN_WIDTH), 70 + log2n, dev).requires_grad_()
+        gy = torch.randn(rows, LN_WIDTH, device=dev)
+        with torch.no_grad():
+            ms = timed(lambda: ln(x), 3)
+        gbs = 8.0 * rows * LN_WIDTH / ms / 1e6
+        hbm["kernels"][f"pam_ln_fwd_2^{log2n}"] = {"GBps": gbs, "frac": gbs / peak_gbs, "bytes_per_element": 8}
+        y = ln(x)
+        ms = timed(lambda: torch.autograd.grad(y, (x, ln.weight, ln.bias), gy, retain_graph=True), 3)
+        gbs = 12.0 * rows * LN_WIDTH / ms / 1e6
+        hbm["kernels"][f"pam_ln_bwd_2^{log2n}"] = {"GBps": gbs, "frac": gbs / peak_gbs, "bytes_per_element": 12}
+        del x, gy, y
+    out["hbm_kernels"] = hbm
+    return out
 
 
 # ---- single kernels, for profilers -------------------------------------------------------------------
@@ -340,37 +440,46 @@ def run_case(args):
     from pam_b200 import cuda_bindings as cb
     dev = torch.device("cuda", 0)
     g = torch.Generator().manual_seed(7)
-    n = args.size
-    if args.case in ("gemm", "gemm_specials"):
-        A, B = torch.randn(n, n, generator=g), torch.randn(n, n, generator=g)
+    n = args.size or 4096
+    if args.case in ("gemm", "gemm_specials", "gemm_relu"):
         if args.case == "gemm_specials":       # 1% zeros / denormals / +-1e30 / +-1e-30
-            vals = torch.tensor([0.0, -0.0, 1e-40, -1e-40, 1.4e-45, -1.4e-45, 1e30, -1e30, 1e-30, -1e-30])
-            for t in (A, B):
-                idx = torch.randperm(t.numel(), generator=g)[: t.numel() // 100]
-                t.view(-1)[idx] = vals[torch.arange(idx.numel()) % 10]
-        A, W = A.to(dev), B.to(dev)
+            A, W = randn_with_specials((n, n), 1, dev), randn_with_specials((n, n), 2, dev)
+        elif args.case == "gemm_relu":          # an activation after ReLU times a dense weight
+            A, W = torch.relu(torch.randn(n, n, device=dev)), torch.randn(n, n, device=dev)
+        else:
+            A, W = torch.randn(n, n, device=dev), torch.randn(n, n, device=dev)
         fn, work, unit = (lambda: cb._matmul(0, A, W.T, 1.0, 2)), float(n) ** 3, "MAC"
     elif args.case == "deit_gemms":
-        d = make_inputs(1234, device=dev)
+        d = layer_set_inputs(1234, device=dev)
 
         def fn():
             for X, W, G in zip(d["X"], d["W"], d["G"]):
                 cb._matmul(0, X, W.T, 1.0, 2)
                 cb._matmul(0, G, W, 1.0, 2)
                 cb._matmul(0, X.T, G, 1.0, 2)
-        work, unit = float(MACS_PER_STEP), "MAC"
+        work, unit = float(LAYER_SET_MACS), "MAC"
     elif args.case == "deit_gemms_exact":      # the eight exact-gradient products of the linear-layer set
-        d = make_inputs(1234, device=dev)
+        d = layer_set_inputs(1234, device=dev)
 
         def fn():
             for X, W, G in zip(d["X"], d["W"], d["G"]):
                 cb._matmul_bwd(G, W, X, True, 1.0, 2)            # dX[i,k] = sum_n G[i,n] * slope(X[i,k], W[n,k])
                 cb._matmul_bwd(X.T, G, W.T, False, 1.0, 2)       # dW^T[k,n] = sum_i G[i,n] * slope(W[n,k], X[i,k])
-        work, unit = float(MACS_PER_STEP) * 2 / 3, "MAC"
-    elif args.case == "mul":
+        work, unit = float(LAYER_SET_MACS) * 2 / 3, "MAC"
+    elif args.case == "attention_gemms":       # DeiT-tiny attention: 192 x (197x64 . 64x197) and (197x197 . 197x64)
+        q = torch.randn(192, 197, 64, device=dev)
+        k = torch.randn(192, 197, 64, device=dev)
+        p = torch.softmax(torch.randn(192, 197, 197, device=dev), -1)
+
+        def fn():
+            cb._matmul(0, q, k.transpose(1, 2), 1.0, 3)
+            cb._matmul(0, p, q, 1.0, 3)
+        work, unit = 2.0 * 192 * 197 * 197 * 64, "MAC"
+    elif args.case in ("mul", "div"):
         count = 1 << n if n < 40 else n
         a, b = torch.randn(count, device=dev), torch.randn(count, device=dev)
-        fn, work, unit = (lambda: cb.cuda_kernels.pam_fwd(a, b, 1.0)), 12.0 * count, "B"
+        kernel = cb.cuda_kernels.pam_fwd if args.case == "mul" else cb.cuda_kernels.pad_fwd
+        fn, work, unit = (lambda: kernel(a, b, 1.0)), 12.0 * count, "B"
     elif args.case in ("layer_norm_fwd", "layer_norm_bwd"):
         rows = (1 << n if n < 40 else n) // LN_WIDTH
         x = torch.randn(rows, LN_WIDTH, device=dev, requires_grad=True)
@@ -428,45 +537,40 @@ def run_case(args):
 
 # ---- full training steps (BASELINE configs 3 and 4) -----------------------------------------------------
 
-def run_step_case(args):
+def training_step(args, case, rank, world, dev, steps, warmup):
     """One data-parallel training step per iteration: batch upload, forward, backward, gradient
     all-reduce over the ranks (NCCL; summed, as the reference's fairseq path leaves them), fused PAM
-    Adam.  Every rank holds the same parameters and its own batch (seed + rank).  Prints the step
-    time (slowest rank, CUDA events) and the PAM multiply-accumulate rate of the whole job."""
+    Adam.  Every rank holds the same parameters and its own batch (seed + rank).  Returns the step
+    time (slowest rank, CUDA events), the share of the all-reduce and the PAM multiply-accumulate
+    rate of the whole job."""
     import torch.distributed as dist
     import pam_b200 as pam
-    from pam_b200 import _lib, optim, parallel, steps
-    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    dev = torch.device("cuda", local)
-    torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    from pam_b200 import _lib, optim, parallel, steps as workloads
     kw = dict(approx_bwd=not args.exact_bwd)
     g = torch.Generator().manual_seed(1000 + rank)
-    if args.case == "deit_step":
-        cfg, batch = steps.DeitConfig(), 64
-        params = steps.to_device(steps.deit_params(cfg, torch.Generator().manual_seed(5)), dev)
+    if case == "deit_step":
+        cfg, batch = workloads.DeitConfig(), 64
+        params = workloads.to_device(workloads.deit_params(cfg, torch.Generator().manual_seed(5)), dev)
         host = (torch.randn(batch, cfg.channels, cfg.image, cfg.image, generator=g).pin_memory(),
                 torch.randint(0, cfg.classes, (batch,), generator=g).pin_memory())
-        loss_fn = lambda images, labels: steps.deit_loss(pam, params, images, labels, cfg, kw)
-        macs, hyper = 3 * steps.deit_macs(cfg, batch), dict(lr=5e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.05)
-        what = f"DeiT-tiny step, batch {batch} per GPU"
+        loss_fn = lambda images, labels: workloads.deit_loss(pam, params, images, labels, cfg, kw)
+        macs, hyper = 3 * workloads.deit_macs(cfg, batch), dict(lr=5e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.05)
+        what = f"configs[3]: DeiT-tiny step, batch {batch} per GPU"
     else:
-        cfg = steps.TransformerConfig()
-        params = steps.to_device(steps.transformer_params(cfg, torch.Generator().manual_seed(5)), dev)
-        host = tuple(t.pin_memory() for t in steps.transformer_batch(cfg, g))
-        loss_fn = lambda src, prev, tgt: steps.transformer_loss(pam, params, src, prev, tgt, cfg, kw)
-        macs, hyper = 3 * steps.transformer_macs(cfg), dict(lr=5e-4, betas=(0.9, 0.98), eps=1e-8, weight_decay=1e-4)
-        what = "6+6 transformer step, 4096 tokens per GPU"
+        cfg = workloads.TransformerConfig()
+        params = workloads.to_device(workloads.transformer_params(cfg, torch.Generator().manual_seed(5)), dev)
+        host = tuple(t.pin_memory() for t in workloads.transformer_batch(cfg, g))
+        loss_fn = lambda src, prev, tgt: workloads.transformer_loss(pam, params, src, prev, tgt, cfg, kw)
+        macs, hyper = 3 * workloads.transformer_macs(cfg), dict(lr=5e-4, betas=(0.9, 0.98), eps=1e-8, weight_decay=1e-4)
+        what = "configs[2]: 6+6 transformer step, 4096 tokens per GPU"
     leaves = list(params.values())
     opt = optim.Adam(leaves, opt_functional_cfg="pam", **hyper)
     launches0 = None
-    times, losses = [], []
-    for it in range(args.warmup + args.steps):
-        if it == args.warmup:
+    times, reduce_times, losses = [], [], []
+    for it in range(warmup + steps):
+        if it == warmup:
             launches0 = _lib.lib().pamk_launch_count()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0, e1, r0, r1 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -475,76 +579,125 @@ def run_step_case(args):
         opt.zero_grad(set_to_none=True)
         loss = loss_fn(*batch_dev)
         loss.backward()
+        r0.record()
         parallel.all_reduce_gradients(leaves)
+        r1.record()
         opt.step()
         e1.record()
         torch.cuda.synchronize()
-        if it >= args.warmup:
+        if it >= warmup:
             times.append(e0.elapsed_time(e1))
+            reduce_times.append(r0.elapsed_time(r1))
         losses.append(float(loss.detach()))
     ms = parallel.max_over_ranks(sum(times) / len(times), dev)
-    launches = (_lib.lib().pamk_launch_count() - launches0) / max(1, args.steps)
+    reduce_ms = parallel.max_over_ranks(sum(reduce_times) / len(reduce_times), dev)
+    launches = (_lib.lib().pamk_launch_count() - launches0) / max(1, steps)
+    del opt, params, leaves
+    torch.cuda.empty_cache()
+    return {"workload": what, "approx_bwd": not args.exact_bwd, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms, "all_reduce_ms": reduce_ms, "all_reduce_share": reduce_ms / ms,
+            "PAM_MAC_per_s": macs * world / (ms * 1e-3), "MAC_per_step_per_gpu": macs,
+            "library_launches_per_step": launches, "loss_first": losses[0], "loss_last": losses[-1]}
+
+
+def run_step_case(args):
+    import torch.distributed as dist
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    res = training_step(args, args.case, rank, world, dev, args.steps, args.warmup)
     if rank == 0:
-        print(json.dumps({"case": args.case, "workload": what, "approx_bwd": not args.exact_bwd, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                          "ms_per_step": ms, "PAM_MAC_per_s": macs * world / (ms * 1e-3), "MAC_per_step_per_gpu": macs,
-                          "library_launches_per_step": launches, "loss_first": losses[0], "loss_last": losses[-1],
-                          "params": sum(t.numel() for t in leaves)}))
+        print(json.dumps(dict(res, case=args.case)))
     if world > 1:
         dist.destroy_process_group()
 
 
 # ---- CPU baseline / reference arm ---------------------------------------------------------------------
 
-def cpu_sample(args, target_seconds):
-    """Times the port of the reference's native PyTorch CPU path (oracle/native_port.py) on a bounded
-    sample of the workload: the first `rows` rows of X through every layer, forward and both
-    approx_bwd gradients.  Returns the cpu_baseline object."""
-    from oracle import native_port as N
-    threads = os.cpu_count() or 1
-    torch.set_num_threads(threads)
-    d = make_inputs(1234)
-    rows = args.cpu_rows
-    if rows <= 0:
+def cpu_matmul():
+    """The reference's CPU implementation of the product, row-chunked: pam/native.py `pam_matmul`
+    (staged by oracle/build.py into oracle/_ref/pam_native) when present, else its port
+    (oracle/native_port.py).  Returns (function(A, B) -> C, kind, description)."""
+    from oracle import build as oracle_build
+    native = None
+    try:
+        oracle_build.build_native()
+        native = oracle_build.load_native()
+    except Exception:                                               # noqa: BLE001
+        native = None
+    if native is not None:
+        def run(A, B):
+            # native.pam_matmul materialises [rows, K, cols]; output rows and columns are independent, so
+            # it is fed blocks of about 256 MB of temporaries (identical results, bounded memory)
+            K, N = B.shape
+            cols = max(1, min(N, (64 << 20) // max(1, K)))
+            rows = max(1, (64 << 20) // max(1, K * cols))
+            with torch.no_grad():
+                return torch.cat([torch.cat([native.pam_matmul(A[r:r + rows], B[:, c:c + cols]) for c in range(0, N, cols)], dim=1)
+                                  for r in range(0, A.shape[0], rows)])
+        return run, "reference", "the reference's pam/native.py pam_matmul (float log2/exp2 PAM, PyTorch CPU), evaluated in blocks"
+    from oracle import native_port
+    return (lambda A, B: native_port.matmul(A, B)), "port", "port of pam/native.py (float log2/exp2 PAM) in PyTorch CPU"
+
+
+class CpuSample:
+    """The reference's CPU path on a bounded sample of the headline workload: the first `rows` rows
+    of A against the whole B (same recipe and seeds as rank 0's device inputs)."""
+
+    def __init__(self, n):
+        self.n = n
+        self.run, self.kind, self.what = cpu_matmul()
+        self.threads = os.cpu_count() or 1
+        torch.set_num_threads(self.threads)
+        self.B = randn_with_specials((n, n), 3999, torch.device("cpu"))
+
+    def rows_for(self, seconds):
+        A1 = randn_with_specials((1, self.n), 4000, torch.device("cpu"))
+        self.run(A1, self.B)
         t0 = time.perf_counter()
-        N.matmul(d["X"][0][:8], d["W"][0].T)
-        probe = (time.perf_counter() - t0) / (8 * 192 * 576)          # seconds per MAC
-        per_row = 3 * sum(k * n for k, n in LAYERS) * probe
-        rows = int(max(4, min(TOKENS, target_seconds / max(per_row, 1e-12))))
-    macs = 3 * rows * sum(k * n for k, n in LAYERS)
-    t0 = time.perf_counter()
-    for X, W, G in zip(d["X"], d["W"], d["G"]):
-        N.matmul(X[:rows], W.T)
-        N.matmul(G[:rows], W)
-        N.matmul(X[:rows].T, G[:rows])
-    dt = time.perf_counter() - t0
-    return {"value": macs / dt, "unit": "MAC/s", "cores": threads, "kind": "port",
-            "sample": f"first {rows} of {TOKENS} rows through all four layers, fwd + dX + dW "
-                      f"({macs / 1e6:.0f} M MAC, {dt:.1f} s); port of pam/native.py (float log2/exp2 PAM) in PyTorch CPU",
-            "seconds": dt, "rows": rows}
+        self.run(A1, self.B)
+        per_row = time.perf_counter() - t0
+        return int(max(1, min(self.n, seconds / max(per_row, 1e-9))))
+
+    def measure(self, rows):
+        A = randn_with_specials((rows, self.n), 4000, torch.device("cpu"))
+        t0 = time.perf_counter()
+        self.run(A, self.B)
+        dt = time.perf_counter() - t0
+        macs = float(rows) * self.n * self.n
+        return {"value": macs / dt, "unit": "MAC/s", "cores": self.threads, "kind": self.kind,
+                "sample": f"first {rows} of {self.n} rows of A against the whole B ({macs / 1e9:.2f} G MAC, {dt:.1f} s); {self.what}",
+                "seconds": dt, "rows": rows}
+
+
+def cpu_sample(args, n, target_seconds):
+    sample = CpuSample(n)
+    return sample.measure(args.cpu_rows or sample.rows_for(target_seconds))
 
 
 def run_reference(args):
     if int(os.environ.get("RANK", 0)) != 0:
         return
-    per_step = []
-    base = None
-    for _ in range(args.warmup + args.steps):
-        base = cpu_sample(args, target_seconds=60.0 / max(1, args.steps + args.warmup))
-        per_step.append(base)
-        if not args.cpu_rows:
-            args.cpu_rows = base["rows"]                         # keep the sample fixed across steps
-    timed = per_step[args.warmup:]
-    seconds = sum(b["seconds"] for b in timed)
-    rows = args.cpu_rows
-    macs = 3 * rows * sum(k * n for k, n in LAYERS)
-    value = macs * len(timed) / seconds
-    base = dict(timed[-1], value=value)
+    n = args.size or 16384
+    sample = CpuSample(n)
+    budget = 150.0 / max(1, args.steps + args.warmup)          # the whole run ends within a few minutes
+    rows = args.cpu_rows or sample.rows_for(min(budget, 15.0))  # fixed across steps, independent of --gpus
+    per_step = [sample.measure(rows) for _ in range(args.warmup + args.steps)]
+    timed_steps = per_step[args.warmup:]
+    seconds = sum(b["seconds"] for b in timed_steps)
+    macs = float(rows) * n * n
+    value = macs * len(timed_steps) / seconds
+    base = dict(timed_steps[-1], value=value)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "MAC/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * seconds / len(timed),
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * seconds / len(timed_steps),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (float log2/exp2 PAM)",
         "data": "synthetic",
-        "config": {"workload": "configs[1]: DeiT-tiny PAM linear-layer set (bounded row sample per step)",
+        "config": {"workload": f"configs[4]: scaling sweep, square PAM GEMM M=N=K={n}, fp32, N(0,1) inputs with 1% injected "
+                               "specials; each step a bounded row sample of the same product on the host cores",
                    "rows_per_step": rows},
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": "MAC/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -554,7 +707,7 @@ def run_reference(args):
 
 if __name__ == "__main__":
     a = parse()
-    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, str(ROOT))
     if a.case in ("deit_step", "transformer_step"):
         run_step_case(a)
     elif a.case:

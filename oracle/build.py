@@ -8,6 +8,10 @@
   through a pipe between ref_prelude.h and array_loops.inc straight into g++; no reference
   source is written into this repository.  Skipped when the reference tree is not mounted
   (e.g. on a GPU box, which uses the prebuilt file).
+* ``oracle/_ref/pam_native/`` — the reference's own CPU implementation (pam/native.py and the
+  pam/utils.py it imports), staged unmodified from the mounted tree into this git-ignored build
+  folder so that the benchmark's CPU arm can time the real thing on a machine where the tree is
+  not mounted.  ``load_native()`` imports it; nothing under ``oracle/_ref`` is ever committed.
 
 Neither library is part of the shipped package: only tests, the smoke check and the benchmark's
 CPU-baseline leg load them.
@@ -52,7 +56,45 @@ def build_ref(force: bool = False):
     return out
 
 
+NATIVE_FILES = ("native.py", "utils.py")
+
+
+def build_native(force: bool = False):
+    """Stages the reference's native PyTorch path; returns its folder, or None when neither the
+    reference tree nor an earlier staging exists."""
+    out = HERE / "_ref" / "pam_native"
+    src_dir = REF_CU.parent
+    have = all((out / f).exists() for f in NATIVE_FILES)
+    if not all((src_dir / f).exists() for f in NATIVE_FILES):
+        return out if have else None
+    if force or not have or any((src_dir / f).stat().st_mtime > (out / f).stat().st_mtime for f in NATIVE_FILES):
+        out.mkdir(parents=True, exist_ok=True)
+        for f in NATIVE_FILES:
+            (out / f).write_bytes((src_dir / f).read_bytes())
+        (out / "__init__.py").write_text("")
+    return out
+
+
+def load_native():
+    """The staged reference module ``native`` (pam/native.py), or None when it was never staged."""
+    import importlib.util
+    out = HERE / "_ref" / "pam_native"
+    if not all((out / f).exists() for f in NATIVE_FILES):
+        return None
+    name = "pam_reference_native"
+    if name in sys.modules:
+        return sys.modules[name].native
+    spec = importlib.util.spec_from_file_location(name, out / "__init__.py", submodule_search_locations=[str(out)])
+    pkg = importlib.util.module_from_spec(spec)
+    sys.modules[name] = pkg
+    spec.loader.exec_module(pkg)
+    import importlib
+    pkg.native = importlib.import_module(name + ".native")
+    return pkg.native
+
+
 if __name__ == "__main__":
     force = "--force" in sys.argv
     print(build_oracle(force))
     print(build_ref(force))
+    print(build_native(force))

@@ -17,10 +17,13 @@
 //     row-/column-major combinations of the reference become two loader variants per side), and
 //     every element's exponent is tested against the safe band;
 //   * the reference's per-product range rule (flush below 1e-37, NaN above 1e37 or for
-//     inf/NaN; epfml/pam pam/cuda_kernels.cu:24-37) is hoisted: when every element of the slab has
-//     its exponent in a band that keeps all products in range, the slab runs the two-instruction
-//     loop; otherwise it runs a loop that evaluates the true fp32 product and applies the rule
-//     exactly.  Either way every product equals the reference's bit for bit;
+//     inf/NaN; epfml/pam pam/cuda_kernels.cu:24-37) is hoisted.  A slab whose elements all have their
+//     exponent in a band that keeps every product in range runs the two-instruction loop.  In any other
+//     slab the choice is made per k line: a line without out-of-band elements still costs two
+//     instructions per product; a line whose largest magnitudes cannot multiply beyond the pass range
+//     evaluates the true product only to decide "flush or add" (four instructions); only a line
+//     that could overflow, or holds an inf / NaN, applies the full three-way rule.  Either way every
+//     product equals the reference's bit for bit;
 //   * each output is summed by one thread, strictly in k order, from +0.0f — the same order as
 //     the reference's kernel (cuda_kernels.cu:608-629), so without split-K the sums are
 //     bit-identical too.
@@ -29,18 +32,6 @@
 // product (pam_matmul_bwd_kernel, cuda_kernels.cu:729-832).
 #include "common.cuh"
 #include "pam_scalar.cuh"
-
-#ifndef PAMK_IADD3
-#define PAMK_IADD3 0
-#endif
-// Timing experiment only (never set in shipped builds): skip the exponent-range bookkeeping and run
-// the two-instruction loop unconditionally, to measure what the bookkeeping costs.
-#ifndef PAMK_FAST_UNROLL
-#define PAMK_FAST_UNROLL 8
-#endif
-#ifndef PAMK_EXPERIMENT_NOSTATS
-#define PAMK_EXPERIMENT_NOSTATS 0
-#endif
 
 namespace pamk {
 namespace {
@@ -147,10 +138,10 @@ __device__ __forceinline__ void load_slab(float (&r)[NT * 4], const MatArg& m, c
 template <class T, int R, int NT, bool KC>
 struct SlabWalker {
     const float* ptr[NT];
-    int step;                                        // elements to advance per slab
+    int64_t step;                                    // elements to advance per slab
 
     __device__ __forceinline__ void init(const MatArg& m, const float* base, int row0, int rows, int k_begin, int tid) {
-        step = KC ? T::BK : T::BK * (int)m.sk;
+        step = KC ? (int64_t)T::BK : (int64_t)T::BK * m.sk;
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
             const int id = tid + t * T::kThreads;
@@ -194,16 +185,21 @@ __device__ __forceinline__ void store_slab(float* s, const float (&r)[NT * 4], i
     }
 }
 
-// ---- which loop a slab may run ---------------------------------------------------------------------
+// ---- which loop a slab, and each of its k lines, may run ---------------------------------------------
 // Products of normal finite numbers satisfy 2^(ea+eb-254) <= |a*b| <= 2^(ea+eb-252) (ea, eb the
-// biased exponents), so if every element of both operand slabs has its exponent field in the band
-// [66, 187] every product lies in [2^-122, 2^122], inside the reference's pass range (1e-37, 1e37):
-//   kFast:  all elements in the band: add the bit patterns, accumulate.
-//   kFlush: some element below the band (zero, denormal, tiny) but none above it: no product can
-//           reach 1e37 and no operand is inf / NaN; evaluate the true product, skip what flushes.
-//   kFull:  some element above the band: the complete three-way rule.
-// The band test is one three-input add and one unsigned max per element: 2 * bits drops the sign,
-// minus twice the band's lower bound makes "below" wrap around to huge values.
+// biased exponents), so if both factors have their exponent field in the band [66, 187] the product
+// lies in [2^-122, 2^122], inside the reference's pass range (1e-37, 1e37), and the range rule
+// (cuda_kernels.cu:24-37) returns the integer sum.  The band test is one three-input add and one
+// unsigned max per element: 2 * bits drops the sign, minus twice the band's lower bound makes "below"
+// wrap around to huge values.
+//   * A slab whose elements are all in the band runs the two-instruction loop.
+//   * Otherwise the staging threads that hold out-of-band elements record, per k line, that the line
+//     is dirty and whether it holds an element above the band.  A clean line of a dirty slab still
+//     costs two instructions per product.
+//   * A dirty line evaluates the true fp32 product.  It can skip the overflow test when the largest
+//     magnitudes of its two operand lines cannot multiply beyond 1e37 and neither holds an inf / NaN
+//     (|a * b| rounded grows with |a| and |b|, so the two maxima bound every product of the line):
+//     four instructions per product, "flush or add".  Only the remaining lines apply the full rule.
 enum Path { kFast = 0, kFlush = 1, kFull = 2 };
 
 constexpr uint32_t kBandLo2 = 2u * (66u << 23);                // 2 * smallest in-band magnitude
@@ -220,15 +216,29 @@ __device__ __forceinline__ uint32_t band_excess(const float (&r)[N], uint32_t vm
     return vmax;
 }
 
-template <int N>
-__device__ __forceinline__ unsigned above_band(const float (&r)[N]) {
-    unsigned any = 0;
+// Position of element c of staging task `id` inside the slab: its k line.
+template <class T, int R, bool KC>
+__device__ __forceinline__ int slab_line(int id, int c) {
+    return KC ? (id % (T::BK / 4)) * 4 + c : id / (R / 4);
+}
+
+// k lines of this thread's staged elements that hold an out-of-band element (low 16 bits) and an
+// element above the band (bits 16..31).
+template <class T, int R, int NT, bool KC>
+__device__ __forceinline__ unsigned dirty_lines(const float (&r)[NT * 4], int tid) {
+    unsigned lines = 0;
 #pragma unroll
-    for (int c = 0; c < N; ++c) {
-        const uint32_t b = (uint32_t)f2i(r[c]);
-        any |= (b + b >= kBandHi2) ? 2u : 0u;
-    }
-    return any;
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint32_t b = (uint32_t)f2i(r[t * 4 + c]);
+            const uint32_t m2 = b + b;
+            if (m2 - kBandLo2 >= kBandSpan2) {
+                const unsigned bit = 1u << slab_line<T, R, KC>(tid + t * T::kThreads, c);
+                lines |= bit | (m2 >= kBandHi2 ? bit << 16 : 0u);
+            }
+        }
+    return lines;
 }
 
 template <int MODE, class T, bool A_KC, bool B_KC, bool VEC>
@@ -236,10 +246,11 @@ __global__ void __launch_bounds__(T::kThreads, MODE == kPam || MODE == kStd ? T:
 gemm_kernel(const GemmParams p) {
     constexpr int BM = T::BM, BN = T::BN, BK = T::BK, MT = T::MT;
     // (the variant with both operands contiguous along their row index spills registers at 8)
-    constexpr int kFastUnroll = (!A_KC && !B_KC) || PAMK_FAST_UNROLL > BK ? BK : PAMK_FAST_UNROLL;
+    constexpr int kFastUnroll = (!A_KC && !B_KC) || 8 > BK ? BK : 8;
     __shared__ __align__(16) float As[2][BK * row_stride(BM)];
     __shared__ __align__(16) float Bs[2][BK * row_stride(BN)];
-    __shared__ unsigned flags[3];   // per slab: bit 0 = an element outside the band, bit 1 = one above it
+    __shared__ unsigned lines[3];   // per slab: bit k = k line holds an out-of-band element, bit 16 + k = one above the band
+    __shared__ unsigned overflow_lines;   // bit k = some product of k line may leave the pass range
 
     const int tid = threadIdx.x;
     const int tx = tid % T::TX, ty = tid / T::TX;
@@ -276,20 +287,8 @@ gemm_kernel(const GemmParams p) {
         }
     }
 
-    if (MODE == kPam && tid < 3) flags[tid] = 0;
+    if (MODE == kPam && tid < 3) lines[tid] = 0;
 
-    // Two equivalent forms of the product's integer add.  Default: the A slab is pre-biased while it
-    // is staged, so a product is a two-input add.  PAMK_IADD3: operands stay raw and the bias is the
-    // third input of the add (measured slower on B200: the extra register read costs more than the
-    // staging pass saves).
-#if PAMK_IADD3
-    const int32_t nbias = isub(0, p.bias_sub);
-#define PAMK_PRODUCT(x, y) iadd3((x), (y), nbias)
-#define PAMK_RAW(x) i2f(x)
-#else
-#define PAMK_PRODUCT(x, y) iadd((x), (y))
-#define PAMK_RAW(x) i2f(iadd((x), p.bias_sub))
-#endif
     float ra[T::kTasksA * 4], rb[T::kTasksB * 4];
     SlabWalker<T, BM, T::kTasksA, A_KC> walk_a;
     SlabWalker<T, BN, T::kTasksB, B_KC> walk_b;
@@ -307,19 +306,18 @@ gemm_kernel(const GemmParams p) {
         }
     };
     auto stage_store = [&](int buf, int slot) {
-        if (MODE == kPam && !PAMK_EXPERIMENT_NOSTATS) {
+        if (MODE == kPam) {
             // clean warps (the common case) pay the band test and one vote; only a warp that holds
-            // an out-of-band element classifies it and reports to the slab's flag word
+            // an out-of-band element locates it and reports its k line to the slab's word
             const bool out = band_excess(rb, band_excess(ra, 0u)) >= kBandSpan2;
             if (__any_sync(0xffffffffu, out)) {
-                unsigned f = out ? (1u | above_band(ra) | above_band(rb)) : 0u;
+                unsigned f = out ? (dirty_lines<T, BM, T::kTasksA, A_KC>(ra, tid) | dirty_lines<T, BN, T::kTasksB, B_KC>(rb, tid)) : 0u;
                 f = __reduce_or_sync(0xffffffffu, f);
-                if ((tid & 31) == 0) atomicOr(&flags[slot], f);
+                if ((tid & 31) == 0) atomicOr(&lines[slot], f);
             }
-#if !PAMK_IADD3
+            // the A side is pre-biased (bits - (0x3f800000 - offset)) so that a product is a two-input add
 #pragma unroll
             for (int c = 0; c < T::kTasksA * 4; ++c) ra[c] = i2f(isub(f2i(ra[c]), p.bias_sub));
-#endif
         }
         store_slab<T, BM, T::kTasksA, A_KC>(As[buf], ra, tid);
         store_slab<T, BN, T::kTasksB, B_KC>(Bs[buf], rb, tid);
@@ -330,16 +328,18 @@ gemm_kernel(const GemmParams p) {
     if (slabs > 0) stage_store(0, 0);
     __syncthreads();
 
-    for (int s = 0; s < slabs; ++s) {
+    // One slab.  (Written as a lambda called from the loop below: in this form the compiler's register
+    // allocation of the 128x128 kernels needs no spills, which the same statements placed directly in
+    // the loop body do.)
+    auto slab_iteration = [&](int s) {
         const int buf = s & 1;
         const bool more = s + 1 < slabs;
         if (more) stage_load(k_begin + (s + 1) * BK);
-        int path = kFast;
-        if (MODE == kPam && !PAMK_EXPERIMENT_NOSTATS) {
-            const unsigned f = flags[s % 3];
-            path = f == 0 ? kFast : ((f & 2u) ? kFull : kFlush);
-            // the slot two slabs ahead was last read before the previous barrier: reset it now
-            if (tid == 0) flags[(s + 2) % 3] = 0;
+        unsigned dirty = 0;
+        if (MODE == kPam) {
+            dirty = lines[s % 3];
+            // the word two slabs ahead was last read before the previous barrier: reset it now
+            if (tid == 0) lines[(s + 2) % 3] = 0;
         }
         const float* as = As[buf];
         const float* bs = Bs[buf];
@@ -352,49 +352,97 @@ gemm_kernel(const GemmParams p) {
         const int a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};                              \
         const int b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 
-        if (MODE == kPam && path == kFast) {
+        if (MODE == kPam && dirty == 0) {
 #pragma unroll kFastUnroll
             for (int kk = 0; kk < BK; ++kk) {
                 PAMK_FRAGMENTS(kk)
 #pragma unroll
                 for (int i = 0; i < MT; ++i)
 #pragma unroll
-                    for (int j = 0; j < MT; ++j) acc[i][j] = fadd(acc[i][j], i2f(PAMK_PRODUCT(a[i], b[j])));
+                    for (int j = 0; j < MT; ++j) acc[i][j] = fadd(acc[i][j], i2f(iadd(a[i], b[j])));
             }
-        } else if (MODE == kPam && path == kFlush) {
-            // (deeper unrolling gains 2 % on all-flush inputs and loses 40 % when slabs alternate
-            // between the three loops: the instruction cache does not hold all of them unrolled)
-#pragma unroll 2
-            for (int kk = 0; kk < BK; ++kk) {
-                PAMK_FRAGMENTS(kk)
-                float araw[MT];          // a[] holds pre-biased patterns; the product needs the values
+        } else if constexpr (MODE == kPam) {
+            // lines that hold an element above the band: can a product leave the pass range?
+            unsigned full = 0;
+            if (dirty >> 16) {                                  // (uniform: read from shared memory after a barrier)
+                constexpr int kLanes = T::kThreads / BK;        // threads that share one k line
+                const int line = tid / kLanes, lane = tid % kLanes;
+                if (tid == 0) overflow_lines = 0;
+                __syncthreads();
+                // (every thread takes part, whatever its line: the shuffles below name all 32 lanes)
+                uint32_t hi_a = 0, hi_b = 0;                    // magnitudes compare like their bit patterns; inf / NaN are largest
+                for (int q = lane; q < BM; q += kLanes) {
+                    hi_a = max(hi_a, (uint32_t)iadd(f2i(as[line * row_stride(BM) + q]), p.bias_sub) & 0x7fffffffu);
+                    hi_b = max(hi_b, (uint32_t)f2i(bs[line * row_stride(BN) + q]) & 0x7fffffffu);
+                }
 #pragma unroll
-                for (int i = 0; i < MT; ++i) araw[i] = PAMK_RAW(a[i]);
-#pragma unroll
-                for (int i = 0; i < MT; ++i)
-#pragma unroll
-                    for (int j = 0; j < MT; ++j) {
-                        const float mag = fabsf(fmul(araw[i], i2f(b[j])));
-                        if (mag > i2f(kFlushBits)) acc[i][j] = fadd(acc[i][j], i2f(PAMK_PRODUCT(a[i], b[j])));
-                    }
+                for (int d = 1; d < kLanes; d <<= 1) {
+                    hi_a = max(hi_a, __shfl_xor_sync(0xffffffffu, hi_a, d));
+                    hi_b = max(hi_b, __shfl_xor_sync(0xffffffffu, hi_b, d));
+                }
+                // (an inf or NaN maximum makes the product inf or NaN: not <= the pass bound)
+                if (lane == 0 && !(fmul(i2f((int32_t)hi_a), i2f((int32_t)hi_b)) <= i2f(kPassBits))) atomicOr(&overflow_lines, 1u << line);
+                __syncthreads();
+                full = overflow_lines;
             }
-        } else {
+            const unsigned all_lines = (1u << BK) - 1u;
+            if (__popc(dirty & all_lines) * 4 >= BK * 3 && full == 0) {
+                // most lines dirty, none can overflow (e.g. an operand that is half zeros): "flush or add"
+                // for the whole slab in one unrolled loop (it is exact for clean lines too)
 #pragma unroll 2
-            for (int kk = 0; kk < BK; ++kk) {
-                PAMK_FRAGMENTS(kk)
-                if constexpr (MODE == kPam) {
-                    float araw[MT];
+                for (int kk = 0; kk < BK; ++kk) {
+                    PAMK_FRAGMENTS(kk)
+                    float araw[MT];          // a[] holds pre-biased patterns; the rule needs the values
 #pragma unroll
-                    for (int i = 0; i < MT; ++i) araw[i] = PAMK_RAW(a[i]);
+                    for (int i = 0; i < MT; ++i) araw[i] = i2f(iadd(a[i], p.bias_sub));
 #pragma unroll
                     for (int i = 0; i < MT; ++i)
 #pragma unroll
                         for (int j = 0; j < MT; ++j) {
                             const float mag = fabsf(fmul(araw[i], i2f(b[j])));
-                            const float prod = mag <= i2f(kPassBits) ? i2f(PAMK_PRODUCT(a[i], b[j])) : quiet_nan();
-                            if (!(mag <= i2f(kFlushBits))) acc[i][j] = fadd(acc[i][j], prod);
+                            if (mag > i2f(kFlushBits)) acc[i][j] = fadd(acc[i][j], i2f(iadd(a[i], b[j])));
                         }
-                } else if constexpr (MODE == kStd) {
+                }
+            } else {
+                // (one copy of each body: with the bodies unrolled together the loop measured a third slower)
+#pragma unroll 1
+                for (int kk = 0; kk < BK; ++kk) {
+                    PAMK_FRAGMENTS(kk)
+                    if (!((dirty >> kk) & 1u)) {
+#pragma unroll
+                        for (int i = 0; i < MT; ++i)
+#pragma unroll
+                            for (int j = 0; j < MT; ++j) acc[i][j] = fadd(acc[i][j], i2f(iadd(a[i], b[j])));
+                    } else {
+                        float araw[MT];
+#pragma unroll
+                        for (int i = 0; i < MT; ++i) araw[i] = i2f(iadd(a[i], p.bias_sub));
+                        if (!((full >> kk) & 1u)) {
+#pragma unroll
+                            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                                for (int j = 0; j < MT; ++j) {
+                                    const float mag = fabsf(fmul(araw[i], i2f(b[j])));
+                                    if (mag > i2f(kFlushBits)) acc[i][j] = fadd(acc[i][j], i2f(iadd(a[i], b[j])));
+                                }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                                for (int j = 0; j < MT; ++j) {
+                                    const float mag = fabsf(fmul(araw[i], i2f(b[j])));
+                                    const float prod = mag <= i2f(kPassBits) ? i2f(iadd(a[i], b[j])) : quiet_nan();
+                                    if (!(mag <= i2f(kFlushBits))) acc[i][j] = fadd(acc[i][j], prod);
+                                }
+                        }
+                    }
+                }
+            }
+        } else if constexpr (MODE != kPam) {
+#pragma unroll 2
+            for (int kk = 0; kk < BK; ++kk) {
+                PAMK_FRAGMENTS(kk)
+                if constexpr (MODE == kStd) {
 #pragma unroll
                     for (int i = 0; i < MT; ++i)
 #pragma unroll
@@ -416,7 +464,8 @@ gemm_kernel(const GemmParams p) {
 
         if (more) stage_store(buf ^ 1, (s + 1) % 3);
         __syncthreads();
-    }
+    };
+    for (int s = 0; s < slabs; ++s) slab_iteration(s);
 
     // ---- epilogue ----------------------------------------------------------------------------
     float* Cz = p.C + ((int64_t)sp * p.batch + z) * ((int64_t)p.M * p.N);
