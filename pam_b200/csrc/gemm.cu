@@ -648,6 +648,13 @@ int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspa
         if (split_k != 0) return PAMK_ERR_WORKSPACE;         // an explicit split needs its scratch
         pl = make_plan(mode, p.batch, p.M, p.N, p.K, 1);     // automatic: fall back to no split
     }
+    // the M tiles ride on grid.y (at most 65535): a very tall product planned with a small tile moves to
+    // the 128x128 tile, which reaches 8.3 M rows
+    if (pl.tile != kTileLarge && (p.M + (pl.tile == kTileTiny ? TileTiny::BM : TileSmall::BM) - 1) /
+                                         (pl.tile == kTileTiny ? TileTiny::BM : TileSmall::BM) > 65535) {
+        const int splits = pl.splits;
+        pl = plan_for<TileLarge>(mode, p.batch, p.M, p.N, p.K, splits);
+    }
     const int bm = pl.tile == kTileTiny ? TileTiny::BM : (pl.tile == kTileSmall ? TileSmall::BM : TileLarge::BM);
     const int bn = pl.tile == kTileTiny ? TileTiny::BN : (pl.tile == kTileSmall ? TileSmall::BN : TileLarge::BN);
     const int bk = pl.tile == kTileTiny ? TileTiny::BK : (pl.tile == kTileSmall ? TileSmall::BK : TileLarge::BK);

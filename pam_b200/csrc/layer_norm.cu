@@ -150,38 +150,87 @@ constexpr int min_ctas(int slots, bool backward) {
     return slots <= 8 ? (backward ? 6 : 10) : (slots <= 16 ? (backward ? 4 : 6) : 1);
 }
 
+// Rows one warp handles together.  The per-row scalar chain (variance -> log2 -> half -> exp2 ->
+// exact divisor thresholds) costs more instructions than the elementwise work of a narrow row; with
+// several rows in flight lane L evaluates the chain of row L % kRows only, so the warp pays for one
+// chain per group instead of one per row, and the results travel back by shuffle.  Every row is
+// still summed and evaluated exactly as if it were alone.
+__host__ __device__ constexpr int rows_per_warp(int slots) { return slots <= 8 ? 4 : (slots <= 16 ? 2 : 1); }
+
 template <int VEC, int NCH, bool FULL>
-__global__ void __launch_bounds__(kThreads, min_ctas(VEC * NCH, false)) ln_fwd_kernel(const LnArgs a) {
+__global__ void __launch_bounds__(kThreads, VEC * NCH <= 16 ? 6 : 1) ln_fwd_kernel(const LnArgs a) {
+    constexpr int kRows = rows_per_warp(VEC * NCH);
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
     const Shared sh = make_shared(a.nf, a.off);
-    for (int64_t row = warp; row < a.rows; row += nwarps) {
-        RowRegs<VEC, NCH> c;
-        load_row<VEC, NCH, FULL>(c, a.x + row * a.width, a.width, lane, 0.0f);
-        RowStats st;
-        centre_and_stats<VEC, NCH, FULL>(c, st, a, sh, lane);
-        const Divisor by_denom = make_divisor(st.denom, a.off);
-        // weight and bias are re-read per row (they stay in L1) rather than held in registers for
-        // the whole kernel: the registers buy more resident warps
+    for (int64_t row0 = warp * kRows; row0 < a.rows; row0 += nwarps * kRows) {
+        RowRegs<VEC, NCH> c[kRows];
+        float s1[kRows], s2[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            // (a row beyond the end is computed on the last row's data and not stored)
+            const int64_t row = row0 + r < a.rows ? row0 + r : a.rows - 1;
+            load_row<VEC, NCH, FULL>(c[r], a.x + row * a.width, a.width, lane, 0.0f);
+        }
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) s = fadd(s, c[r].v[i]);
+            s1[r] = warp_sum(s);
+            const float mu = div_by(s1[r], sh.by_n);
+            s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) {
+                c[r].v[i] = live<VEC, NCH, FULL>(i, a.width, lane) ? fadd(c[r].v[i], -mu) : 0.0f;
+                s = fadd(s, mul(c[r].v[i], c[r].v[i], a.off));
+            }
+            s2[r] = warp_sum(s);
+        }
+        // the scalar chain of row (lane % kRows), then every row's divisor to every lane
+        RowStats mine;
+        mine.s2 = s2[0];
+#pragma unroll
+        for (int r = 1; r < kRows; ++r) mine.s2 = (lane % kRows) == r ? s2[r] : mine.s2;
+        finish_stats(mine, a, sh);
+        const Divisor my_divisor = make_divisor(mine.denom, a.off);
+        // weight and bias are re-read per row group (they stay in L1) rather than held in registers
+        // for the whole kernel: the registers buy more resident warps
         RowRegs<VEC, NCH> p;
         if (a.w) load_row<VEC, NCH, FULL>(p, a.w, a.width, lane, 1.0f);
 #pragma unroll
-        for (int i = 0; i < NCH * VEC; ++i) {
-            const float y = div_by(c.v[i], by_denom);
-            c.v[i] = a.w ? mul(y, p.v[i], a.off) : y;
+        for (int r = 0; r < kRows; ++r) {
+            Divisor by_denom;
+            by_denom.flush_max = __shfl_sync(0xffffffffu, my_divisor.flush_max, r);
+            by_denom.pass_max = __shfl_sync(0xffffffffu, my_divisor.pass_max, r);
+            by_denom.sub = __shfl_sync(0xffffffffu, my_divisor.sub, r);
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) {
+                const float y = div_by(c[r].v[i], by_denom);
+                c[r].v[i] = a.w ? mul(y, p.v[i], a.off) : y;
+            }
         }
         if (a.b) {
             load_row<VEC, NCH, FULL>(p, a.b, a.width, lane, 0.0f);
 #pragma unroll
-            for (int i = 0; i < NCH * VEC; ++i) c.v[i] = fadd(c.v[i], p.v[i]);
+            for (int r = 0; r < kRows; ++r)
+#pragma unroll
+                for (int i = 0; i < NCH * VEC; ++i) c[r].v[i] = fadd(c[r].v[i], p.v[i]);
         }
-        store_row<VEC, NCH, FULL>(c, a.out + row * a.width, a.width, lane);
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+            if (row0 + r < a.rows) store_row<VEC, NCH, FULL>(c[r], a.out + (row0 + r) * a.width, a.width, lane);
     }
 }
 
+// (four rows of a narrow layout need 158 registers and run 12 warps per SM; two rows at 96 registers
+// and 20 warps measured 5 % slower)
+__host__ __device__ constexpr int rows_per_warp_bwd(int slots) { return slots <= 8 ? 4 : (slots <= 16 ? 2 : 1); }
+
 template <int VEC, int NCH, bool APPROX, bool FULL>
-__global__ void __launch_bounds__(kThreads, min_ctas(VEC * NCH, true)) ln_bwd_kernel(const LnArgs a) {
+__global__ void __launch_bounds__(kThreads, VEC * NCH <= 16 ? 3 : 1) ln_bwd_kernel(const LnArgs a) {
+    constexpr int kRows = rows_per_warp_bwd(VEC * NCH);
     __shared__ float stage[kWarpsPerCta][NCH * VEC][32];
     const int lane = threadIdx.x & 31;
     const int wid = threadIdx.x >> 5;
@@ -195,58 +244,106 @@ __global__ void __launch_bounds__(kThreads, min_ctas(VEC * NCH, true)) ln_bwd_ke
 #pragma unroll
     for (int i = 0; i < NCH * VEC; ++i) dw.v[i] = db.v[i] = 0.0f;
 
-    for (int64_t row = warp; row < a.rows; row += nwarps) {
-        RowRegs<VEC, NCH> c, g;
-        load_row<VEC, NCH, FULL>(c, a.x + row * a.width, a.width, lane, 0.0f);
-        load_row<VEC, NCH, FULL>(g, a.dy + row * a.width, a.width, lane, 0.0f);
+    // kRows rows per pass: lane L evaluates the two scalar chains of row L % kRows only (see
+    // rows_per_warp); rows are accumulated into dw / db in row order, as a one-row-per-pass walk would.
+    for (int64_t row0 = warp * kRows; row0 < a.rows; row0 += nwarps * kRows) {
+        RowRegs<VEC, NCH> c[kRows], g[kRows];
+        float s1[kRows], s2[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const int64_t row = row0 + r < a.rows ? row0 + r : a.rows - 1;     // (beyond the end: computed, not stored)
+            load_row<VEC, NCH, FULL>(c[r], a.x + row * a.width, a.width, lane, 0.0f);
+            load_row<VEC, NCH, FULL>(g[r], a.dy + row * a.width, a.width, lane, 0.0f);
+        }
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) s = fadd(s, c[r].v[i]);
+            s1[r] = warp_sum(s);
+            const float mu = div_by(s1[r], sh.by_n);
+            s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) {
+                c[r].v[i] = live<VEC, NCH, FULL>(i, a.width, lane) ? fadd(c[r].v[i], -mu) : 0.0f;
+                s = fadd(s, mul(c[r].v[i], c[r].v[i], a.off));
+            }
+            s2[r] = warp_sum(s);
+        }
+        const int my_row = lane % kRows;
         RowStats st;
-        centre_and_stats<VEC, NCH, FULL>(c, st, a, sh, lane);
-        const Divisor by_denom = make_divisor(st.denom, a.off);
-        const float recip = div_by(1.0f, by_denom);
+        st.s2 = s2[0];
+        st.s1 = s1[0];
+#pragma unroll
+        for (int r = 1; r < kRows; ++r) {
+            st.s2 = my_row == r ? s2[r] : st.s2;
+            st.s1 = my_row == r ? s1[r] : st.s1;
+        }
+        finish_stats(st, a, sh);
+        const Divisor my_divisor = make_divisor(st.denom, a.off);
+        const float my_recip = div_by(1.0f, my_divisor);
 
         // d(out)/d(xn), the division's two gradients; g is overwritten by d_c1
-        float sum_dden = 0.0f;
+        float d_denom[kRows], recip[kRows];
 #pragma unroll
-        for (int i = 0; i < NCH * VEC; ++i) {
-            const bool on = live<VEC, NCH, FULL>(i, a.width, lane);
-            const float xn = div_by(c.v[i], by_denom);
-            float dxn = g.v[i];
-            if (a.w) {
-                if (on) {
-                    dw.v[i] = fadd(dw.v[i], APPROX ? mul(g.v[i], xn, a.off) : mul_bwd(w.v[i], xn, g.v[i], a.off));
-                    db.v[i] = fadd(db.v[i], g.v[i]);
+        for (int r = 0; r < kRows; ++r) {
+            Divisor by_denom;
+            by_denom.flush_max = __shfl_sync(0xffffffffu, my_divisor.flush_max, r);
+            by_denom.pass_max = __shfl_sync(0xffffffffu, my_divisor.pass_max, r);
+            by_denom.sub = __shfl_sync(0xffffffffu, my_divisor.sub, r);
+            recip[r] = __shfl_sync(0xffffffffu, my_recip, r);
+            const float denom = __shfl_sync(0xffffffffu, st.denom, r);
+            const bool row_on = row0 + r < a.rows;
+            float sum_dden = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) {
+                const bool on = live<VEC, NCH, FULL>(i, a.width, lane) && row_on;
+                const float xn = div_by(c[r].v[i], by_denom);
+                float dxn = g[r].v[i];
+                if (a.w) {
+                    if (on) {
+                        dw.v[i] = fadd(dw.v[i], APPROX ? mul(g[r].v[i], xn, a.off) : mul_bwd(w.v[i], xn, g[r].v[i], a.off));
+                        db.v[i] = fadd(db.v[i], g[r].v[i]);
+                    }
+                    dxn = APPROX ? mul(g[r].v[i], w.v[i], a.off) : mul_bwd(xn, w.v[i], g[r].v[i], a.off);
+                } else if (a.partials && on) {
+                    db.v[i] = fadd(db.v[i], g[r].v[i]);
                 }
-                dxn = APPROX ? mul(g.v[i], w.v[i], a.off) : mul_bwd(xn, w.v[i], g.v[i], a.off);
-            } else if (a.partials && on) {
-                db.v[i] = fadd(db.v[i], g.v[i]);
+                const float dden = APPROX ? -mul(div_by(xn, by_denom), dxn, a.off)
+                                          : div_bwd(c[r].v[i], denom, dxn, a.off);
+                if (live<VEC, NCH, FULL>(i, a.width, lane)) sum_dden = fadd(sum_dden, dden);
+                g[r].v[i] = APPROX ? mul(recip[r], dxn, a.off) : mul_bwd(c[r].v[i], recip[r], dxn, 0);
             }
-            const float dden = APPROX ? -mul(div_by(xn, by_denom), dxn, a.off)
-                                      : div_bwd(c.v[i], st.denom, dxn, a.off);
-            if (on) sum_dden = fadd(sum_dden, dden);
-            g.v[i] = APPROX ? mul(recip, dxn, a.off) : mul_bwd(c.v[i], recip, dxn, 0);
+            d_denom[r] = warp_sum(sum_dden);
         }
-        const float d_denom = warp_sum(sum_dden);
 
-        // scalar chain back through pow(v, 0.5) and the variance
-        const float d_e = st.v == 0.0f ? 0.0f : d_denom;
+        // scalar chain back through pow(v, 0.5) and the variance, for row lane % kRows
+        float my_d_denom = d_denom[0];
+#pragma unroll
+        for (int r = 1; r < kRows; ++r) my_d_denom = my_row == r ? d_denom[r] : my_d_denom;
+        const float d_e = st.v == 0.0f ? 0.0f : my_d_denom;
         const float d_m = APPROX ? mul(mul(st.e, ln2, a.off), d_e, a.off) : exp_base_bwd(st.m, d_e, sh.lb2, a.off);
         const float d_l = APPROX ? mul(d_m, 0.5f, a.off) : mul_bwd(st.l, 0.5f, d_m, a.off);
         const float d_v = APPROX ? div(div(d_l, st.v, a.off), ln2, a.off) : log_base_bwd(st.v, d_l, sh.lb2, a.off);
-        const float d_s2 = APPROX ? mul(recip_n, d_v, a.off) : mul_bwd(st.s2, recip_n, d_v, 0);
+        const float my_d_s2 = APPROX ? mul(recip_n, d_v, a.off) : mul_bwd(st.s2, recip_n, d_v, 0);
 
         // c feeds the division and both operands of pam(c, c)
-        float sum_dc = 0.0f;
 #pragma unroll
-        for (int i = 0; i < NCH * VEC; ++i) {
-            const float dsq = APPROX ? mul(d_s2, c.v[i], a.off) : mul_bwd(c.v[i], c.v[i], d_s2, a.off);
-            g.v[i] = fadd(fadd(g.v[i], dsq), dsq);
-            if (live<VEC, NCH, FULL>(i, a.width, lane)) sum_dc = fadd(sum_dc, g.v[i]);
+        for (int r = 0; r < kRows; ++r) {
+            const float d_s2 = __shfl_sync(0xffffffffu, my_d_s2, r);
+            float sum_dc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) {
+                const float dsq = APPROX ? mul(d_s2, c[r].v[i], a.off) : mul_bwd(c[r].v[i], c[r].v[i], d_s2, a.off);
+                g[r].v[i] = fadd(fadd(g[r].v[i], dsq), dsq);
+                if (live<VEC, NCH, FULL>(i, a.width, lane)) sum_dc = fadd(sum_dc, g[r].v[i]);
+            }
+            const float d_mu = -warp_sum(sum_dc);
+            const float d_s1 = APPROX ? mul(recip_n, d_mu, a.off) : mul_bwd(s1[r], recip_n, d_mu, 0);
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) g[r].v[i] = fadd(g[r].v[i], d_s1);
+            if (row0 + r < a.rows) store_row<VEC, NCH, FULL>(g[r], a.out + (row0 + r) * a.width, a.width, lane);
         }
-        const float d_mu = -warp_sum(sum_dc);
-        const float d_s1 = APPROX ? mul(recip_n, d_mu, a.off) : mul_bwd(st.s1, recip_n, d_mu, 0);
-#pragma unroll
-        for (int i = 0; i < NCH * VEC; ++i) g.v[i] = fadd(g.v[i], d_s1);
-        store_row<VEC, NCH, FULL>(g, a.out + row * a.width, a.width, lane);
     }
 
     // per-CTA column sums for dw / db: warps are added in warp order, CTAs by the second kernel

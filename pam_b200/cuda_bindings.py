@@ -168,7 +168,8 @@ def _matmul(kind, A, B, offset, dims, split_k=None, bias=None):
     out = torch.empty((batch, M, N) if dims == 3 else (M, N), dtype=torch.float32, device=device)
     handle = _lib.lib()
     if split_k is None:
-        split_k = 1 if _strict_k_order else handle.pamk_matmul_auto_split(batch, M, N, K)
+        # (the true-multiply product has one tile shape and its own cost model: it is never split here)
+        split_k = 1 if _strict_k_order or kind != _lib.MUL_PAM else handle.pamk_matmul_auto_split(batch, M, N, K)
     ws_ptr, ws_bytes = None, 0
     if split_k > 1:
         ws_bytes = handle.pamk_matmul_workspace_bytes(batch, M, N, split_k)

@@ -160,17 +160,18 @@ def kernel_rowsum(vec, warps=1):
     return rowsum
 
 
-def kernel_colsum(rows_total, grid, warps_per_cta=4, grad_warps=32):
-    """Order of the dweight / dbias sums in the kernel: warp w of CTA c adds its rows
-    (c*4 + w, + grid*4, ...) in order from +0; the four warps of a CTA are added in order; the
-    second kernel's warp j adds the CTA sums j, j + 32, ... in order from +0 and the 32 warp
-    sums are added in order."""
+def kernel_colsum(rows_total, grid, warps_per_cta=4, grad_warps=32, rows_per_warp=1):
+    """Order of the dweight / dbias sums in the kernel: a warp takes `rows_per_warp` consecutive
+    rows per pass (groups g = warp, warp + grid*4, ...) and adds its rows in order from +0; the four
+    warps of a CTA are added in order; the second kernel's warp j adds the CTA sums j, j + 32, ...
+    in order from +0 and the 32 warp sums are added in order."""
     def colsum(t):
         rows, n = t.shape
         nwarps = grid * warps_per_cta
         warp_sums = torch.zeros(nwarps, n)
         for r in range(rows):
-            warp_sums[r % nwarps] = warp_sums[r % nwarps] + t[r]
+            owner = (r // rows_per_warp) % nwarps
+            warp_sums[owner] = warp_sums[owner] + t[r]
         ws = warp_sums.view(grid, warps_per_cta, n)
         cta = ws[:, 0]
         for wdx in range(1, warps_per_cta):

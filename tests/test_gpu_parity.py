@@ -514,6 +514,19 @@ def _ln_vec(width):
     return 4 if width % 4 == 0 else 1
 
 
+def _ln_rows_per_warp(width):
+    """Rows a warp of the backward kernel handles per pass: four for layouts of up to 8 register
+    slots per lane, two up to 16, else one (pam_b200/csrc/layer_norm.cu rows_per_warp_bwd)."""
+    vec = _ln_vec(width)
+    if vec == 4:
+        slots = next(s for cap, s in ((128, 4), (256, 8), (512, 16), (768, 24), (1024, 32)) if width <= cap)
+    elif vec == 2:
+        slots = 6
+    else:
+        slots = 8 if width <= 256 else 32
+    return 4 if slots <= 8 else (2 if slots <= 16 else 1)
+
+
 def _ln_case(pam, dev, rows, width, affine, approx, offset, seed):
     import ln_emulation as E
     g = torch.Generator().manual_seed(seed)
@@ -529,7 +542,7 @@ def _ln_case(pam, dev, rows, width, affine, approx, offset, seed):
     vec = _ln_vec(width)
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     grid = min((rows + 3) // 4, sms * 12)                    # CTAs of the backward kernel
-    chain = E.Chain(offset, E.kernel_rowsum(vec), E.kernel_colsum(rows, grid))
+    chain = E.Chain(offset, E.kernel_rowsum(vec), E.kernel_colsum(rows, grid, rows_per_warp=_ln_rows_per_warp(width)))
     want = chain.run(x, w, b, gy, 1e-5, approx)
     got = (y, xd.grad, wd.grad if affine else None, bd.grad if affine else None)
     return got, want
