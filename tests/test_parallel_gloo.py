@@ -53,9 +53,22 @@ def _worker(rank, world, port, out_dir):
         local_w_grad = lin.weight.grad.clone()
         parallel.all_reduce_gradients(params)
         reduced_w_grad = lin.weight.grad.clone()
+        # the same sum, started bucket by bucket from gradient hooks during the backward pass
+        for prm in params:
+            prm.grad = None
+        buckets = parallel.GradientBuckets(params, bucket_bytes=256)      # tiny buckets: several per step
+        ln(lin(X[lo:hi])).backward(G[lo:hi])
+        buckets.finish()
+        bucketed_w_grad = lin.weight.grad.clone()
+        ln(lin(X[lo:hi])).backward(G[lo:hi])                              # a second step re-arms the buckets
+        buckets.finish()
+        buckets.remove()
+        second_w_grad = lin.weight.grad.clone()
+        lin.weight.grad = reduced_w_grad.clone()
         opt.step()
         slowest = parallel.max_over_ranks(1.0 + rank, torch.device("cpu"))
         torch.save({"rows": (lo, hi), "Y": Y_rows.detach(), "local": local_w_grad, "reduced": reduced_w_grad,
+                    "bucketed": bucketed_w_grad, "second": second_w_grad,
                     "weight": lin.weight.detach().clone(), "gamma": ln.weight.detach().clone(), "slowest": slowest},
                    os.path.join(out_dir, f"rank{rank}.pt"))
         mpatch.undo()
@@ -83,6 +96,9 @@ def test_row_sharding_and_gradient_all_reduce(tmp_path, oracle, monkeypatch):
     # the all-reduce is the sum of the two local gradients, identical on both ranks
     assert torch.equal(r[0]["reduced"], r[1]["reduced"])
     assert torch.equal(r[0]["reduced"], r[0]["local"] + r[1]["local"])
+    # the overlapped, bucketed reduction gives the same sums; a second backward accumulates onto them
+    assert torch.equal(r[0]["bucketed"], r[0]["reduced"]) and torch.equal(r[1]["bucketed"], r[0]["reduced"])
+    assert torch.equal(r[0]["second"], r[1]["second"])
     # after the optimizer step the replicas hold the same parameters
     assert torch.equal(r[0]["weight"], r[1]["weight"]) and torch.equal(r[0]["gamma"], r[1]["gamma"])
     assert not torch.equal(r[0]["weight"], W0)
