@@ -555,24 +555,32 @@ def training_step(args, case, rank, world, dev, steps, warmup):
     import torch.distributed as dist
     import pam_b200 as pam
     from pam_b200 import _lib, optim, parallel, steps as workloads
-    kw = dict(approx_bwd=not args.exact_bwd)
+    # the models are built as the reference's forks build them: every swappable layer from a configuration
+    # string through the factories (pam_b200/models.py), then filled with the seeded parameters
+    from pam_b200 import models
+    cfgs = models.pam_cfgs(approx_bwd=not args.exact_bwd)
     g = torch.Generator().manual_seed(1000 + rank)
     if case == "deit_step":
         cfg, batch = workloads.DeitConfig(), 64
-        params = workloads.to_device(workloads.deit_params(cfg, torch.Generator().manual_seed(5)), dev)
+        model = models.VisionTransformer(cfg, linear_cfg=cfgs["linear"], conv_cfg=cfgs["linear"], norm_cfg=cfgs["norm"],
+                                         functional_cfg=cfgs["function"])
+        model.load_parameters(workloads.deit_params(cfg, torch.Generator().manual_seed(5))).to(dev)
         host = (torch.randn(batch, cfg.channels, cfg.image, cfg.image, generator=g).pin_memory(),
                 torch.randint(0, cfg.classes, (batch,), generator=g).pin_memory())
-        loss_fn = lambda images, labels: workloads.deit_loss(pam, params, images, labels, cfg, kw)
+        loss_fn = lambda images, labels: torch.nn.functional.cross_entropy(model(images), labels)
         macs, hyper = 3 * workloads.deit_macs(cfg, batch), dict(lr=5e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.05)
         what = f"configs[3]: DeiT-tiny step, batch {batch} per GPU"
     else:
         cfg = workloads.TransformerConfig()
-        params = workloads.to_device(workloads.transformer_params(cfg, torch.Generator().manual_seed(5)), dev)
+        model = models.Transformer(cfg, linear_cfg=cfgs["linear"], norm_cfg=cfgs["norm"], functional_cfg=cfgs["function"],
+                                   loss_functional_cfg=cfgs["function"])
+        model.load_parameters(workloads.transformer_params(cfg, torch.Generator().manual_seed(5))).to(dev)
         host = tuple(t.pin_memory() for t in workloads.transformer_batch(cfg, g))
-        loss_fn = lambda src, prev, tgt: workloads.transformer_loss(pam, params, src, prev, tgt, cfg, kw)
+        loss_fn = model.loss
         macs, hyper = 3 * workloads.transformer_macs(cfg), dict(lr=5e-4, betas=(0.9, 0.98), eps=1e-8, weight_decay=1e-4)
         what = "configs[2]: 6+6 transformer step, 4096 tokens per GPU"
-    leaves = list(params.values())
+    params = model
+    leaves = list(model.parameters())
     opt = optim.Adam(leaves, opt_functional_cfg="pam", **hyper)
     buckets = parallel.GradientBuckets(leaves)       # all-reduce per 25 MB bucket, overlapped with the backward pass
     launches0 = None
@@ -603,7 +611,7 @@ def training_step(args, case, rank, world, dev, steps, warmup):
     reduce_ms = parallel.max_over_ranks(sum(reduce_times) / len(reduce_times), dev)
     launches = (_lib.lib().pamk_launch_count() - launches0) / max(1, steps)
     buckets.remove()
-    del opt, params, leaves, buckets
+    del opt, params, model, leaves, buckets
     torch.cuda.empty_cache()
     return {"workload": what, "approx_bwd": not args.exact_bwd, "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": ms, "all_reduce_exposed_ms": reduce_ms, "all_reduce_exposed_share": reduce_ms / ms,

@@ -208,6 +208,33 @@ int pamk_logsumexp_fwd(const float* x, float* y, int64_t rows, int64_t len, floa
 int pamk_logsumexp_bwd(const float* x, const float* dy, float* dx, int64_t rows, int64_t len, float offset,
                        int approx_bwd, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- PAM loss kernels ----------------------------------------------------------------------------------
+ * Label-smoothed negative log-likelihood straight from the logits: the PAM log-softmax
+ * (lprobs = x - logsumexp(x), pam/pam_ops.py:344-347) fused with the gather and the row sum of fairseq's
+ * label_smoothed_nll_loss (fairseq/criterions/label_smoothed_cross_entropy.py:36-54).
+ *   forward:  rows_out[r] = { logsumexp(x_r), -lprobs[r, target_r], -(sum_j lprobs[r, j]) }  ([rows, 3]);
+ *             the last two are 0 for rows whose target is ignore_index (when has_ignore);
+ *   backward: dlogits for d(loss)/d(sum of the nll column) = d_nll and d(loss)/d(sum of the smooth
+ *             column) = d_smooth: -(d_smooth) - (d_nll at the target) plus the logsumexp gradient chain.
+ * The scalar combination loss = pam(1 - eps - eps_i, nll) + pam(eps_i, smooth) stays with the caller.
+ * logits [rows, len] contiguous, target [rows] int64, len <= pamk_softmax_max_len(); workspace as for
+ * pamk_softmax_fwd. */
+int pamk_ls_loss_fwd(const float* logits, const long long* target, float* rows_out, int64_t rows, int64_t len,
+                     int has_ignore, long long ignore_index, float offset,
+                     void* workspace, size_t workspace_bytes, void* stream);
+int pamk_ls_loss_bwd(const float* logits, const long long* target, float* dlogits, int64_t rows, int64_t len,
+                     float d_nll, float d_smooth, int has_ignore, long long ignore_index, float offset, int approx_bwd,
+                     void* workspace, size_t workspace_bytes, void* stream);
+/* Gradient of pam_opt.cross_entropy (pam/pam_opt.py:27-51) in one launch:
+ *   d = pam_softmax(x) - target distribution (hot_prob at the target, cold_prob elsewhere);
+ *   d = pam(d, class_weight[target]) if class_weight; rows with target == ignore_index times 0;
+ *   d = pad(d, mean_rows) if mean_rows > 0 (reduction = "mean"); dlogits = pam(d, *grad_out).
+ * grad_out points to one fp32 value on the device (the incoming gradient of the scalar loss). */
+int pamk_cross_entropy_bwd(const float* logits, const long long* target, const float* class_weight, const float* grad_out,
+                           float* dlogits, int64_t rows, int64_t len, float hot_prob, float cold_prob, float mean_rows,
+                           int has_ignore, long long ignore_index, float offset,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- fused PAM Adam ------------------------------------------------------------------------------
  * Replaces the per-tensor launch chain of the reference's PAM Adam
  * (submodules/fairseq/fairseq/optim/adam.py:226-252 over pam.mul / pam.div / pam.pow):

@@ -70,13 +70,19 @@ __device__ __forceinline__ float load_shift(const float* __restrict__ partials, 
 // ---- rows in registers ---------------------------------------------------------------------------
 struct RowArgs {
     const float* x;
-    const float* g;          // backward: incoming gradient ([rows, len] softmax, [rows] logsumexp)
+    const float* g;          // backward: incoming gradient ([rows, len] softmax, [rows] logsumexp, one value for the losses)
     float* out;              // forward result or dx
     const float* partials;
     int partial_count;
     int64_t rows;
     int len;
     int32_t off;
+    // loss kernels only
+    const long long* target; // [rows] class index of every row
+    const float* weight;     // optional per-class weights (cross-entropy gradient)
+    long long ignore;        // rows whose target equals this contribute nothing (when has_ignore)
+    int has_ignore;
+    float c0, c1, c2;        // label-smoothed loss backward: d nll, d smooth; cross-entropy: hot / cold target probability, row count
 };
 
 // Thread t of a group of WARPS*32 threads holds NCH chunks of VEC consecutive columns: chunk q
@@ -129,7 +135,10 @@ __device__ __forceinline__ float group_sum(float s, float* scratch) {
     return t;
 }
 
-enum Op { kSoftmaxFwd, kSoftmaxBwd, kLseFwd, kLseBwd };
+// kLossFwd / kLossBwd: label-smoothed negative log-likelihood straight from the logits (log-softmax,
+// gather and row sum of fairseq's label_smoothed_nll_loss fused into the logsumexp row pass).
+// kCeBwd: the gradient of pam_opt.cross_entropy (softmax - target distribution, PAM-scaled).
+enum Op { kSoftmaxFwd, kSoftmaxBwd, kLseFwd, kLseBwd, kLossFwd, kLossBwd, kCeBwd };
 
 template <int OP, bool APPROX, int VEC, int NCH, int WARPS>
 __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(const RowArgs a) {
@@ -151,7 +160,7 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
             const bool masked = x.v[i] == -INFINITY;
             const float adj = fadd(scaled_of(x.v[i], off), -shift);
             const float big = exp_base(adj, lb2, off);
-            e.v[i] = (OP == kSoftmaxFwd || OP == kSoftmaxBwd) && masked ? 0.0f : big;
+            e.v[i] = (OP == kSoftmaxFwd || OP == kSoftmaxBwd || OP == kCeBwd) && masked ? 0.0f : big;
             if (R::col(i, t) < a.len) part = fadd(part, e.v[i]);
         }
         const float total = group_sum<WARPS>(part, scratch);
@@ -160,6 +169,73 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
             const Divisor by_total = make_divisor(total, off);
 #pragma unroll
             for (int i = 0; i < NCH * VEC; ++i) e.v[i] = div_by(e.v[i], by_total);
+            e.store(a.out + row * a.len, a.len, t);
+        } else if (OP == kCeBwd) {
+            // pam/pam_opt.py:27-51: (softmax(x) - target distribution), PAM-scaled by the class weight,
+            // the row count (reduction = mean) and the incoming gradient
+            const Divisor by_total = make_divisor(total, off);
+            const long long tgt = a.target[row];
+            const bool ignored = a.has_ignore && tgt == a.ignore;
+            const int hot = ignored ? 0 : (int)tgt;                      // ignored rows use class 0, then times 0
+            const float wt = a.weight ? __ldg(a.weight + hot) : 0.0f;
+            const Divisor by_rows = make_divisor(a.c2, off);
+            const float gout = __ldg(a.g);
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) {
+                const int col = R::col(i, t);
+                float d = fadd(div_by(e.v[i], by_total), -(col == hot ? a.c0 : a.c1));
+                if (a.weight) d = mul(d, wt, off);
+                if (a.has_ignore) d = fmul(d, ignored ? 0.0f : 1.0f);
+                if (a.c2 > 0.0f) d = div_by(d, by_rows);
+                e.v[i] = mul(d, gout, off);
+            }
+            e.store(a.out + row * a.len, a.len, t);
+        } else if (OP == kLossFwd) {
+            // lprobs = x - logsumexp(x); nll = -lprobs[target]; smooth = -(row sum of lprobs)
+            const float lse = div(fadd(shift, log_base(total, lb2, 0)), kLog2e, off);
+            const long long tgt = a.target[row];
+            const bool ignored = a.has_ignore && tgt == a.ignore;
+            float neg_sum = 0.0f, picked = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) {
+                const int col = R::col(i, t);
+                const float neg_lp = fadd(lse, -x.v[i]);                  // -(x - lse), exactly
+                if (col < a.len) neg_sum = fadd(neg_sum, neg_lp);
+                if (col == (int)tgt) picked = neg_lp;
+            }
+            const float smooth = group_sum<WARPS>(neg_sum, scratch);
+            const float nll = group_sum<WARPS>(picked, scratch);          // one thread holds it, the others add +0
+            if (t == 0) {
+                a.out[row * 3] = lse;
+                a.out[row * 3 + 1] = ignored ? 0.0f : nll;
+                a.out[row * 3 + 2] = ignored ? 0.0f : smooth;
+            }
+        } else if (OP == kLossBwd) {
+            // d lprobs = -(d smooth) - (d nll at the target); d lse = -(row sum of d lprobs); then the
+            // logsumexp gradient chain, and x receives both contributions
+            const long long tgt = a.target[row];
+            const bool ignored = a.has_ignore && tgt == a.ignore;
+            const float d_all = ignored ? 0.0f : -a.c1, d_hot = ignored ? 0.0f : fadd(-a.c0, -a.c1);
+            float part_d = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) {
+                const int col = R::col(i, t);
+                if (col < a.len) part_d = fadd(part_d, col == (int)tgt ? d_hot : d_all);
+            }
+            const float gr = -group_sum<WARPS>(part_d, scratch);
+            const float u = fadd(shift, log_base(total, lb2, 0));
+            const float recip = div(1.0f, kLog2e, off);
+            const float d_u = APPROX ? mul(recip, gr, off) : mul_bwd(u, recip, gr, 0);
+            const float d_total = log_base_bwd(total, d_u, lb2, 0);
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) {
+                const int col = R::col(i, t);
+                const float adj = fadd(scaled_of(x.v[i], off), -shift);
+                const float d_adj = APPROX ? mul(mul(e.v[i], kLn2, off), d_total, off)
+                                           : exp_base_bwd(adj, d_total, lb2, off);
+                const float via_lse = APPROX ? mul(d_adj, kLog2e, off) : mul_bwd(x.v[i], kLog2e, d_adj, off);
+                e.v[i] = fadd(col == (int)tgt ? d_hot : d_all, via_lse);
+            }
             e.store(a.out + row * a.len, a.len, t);
         } else if (OP == kLseFwd) {
             // log2 of the row sum runs with offset 0 whatever the call's offset (pam_ops.py:341)
@@ -212,7 +288,7 @@ constexpr int kMaxLen = 12288;
 
 template <int OP, bool APPROX>
 int launch_rows(const RowArgs& a, cudaStream_t st) {
-    const bool vec = (a.len & 3) == 0 && aligned16(a.x) && (OP == kLseFwd || aligned16(a.out)) &&
+    const bool vec = (a.len & 3) == 0 && aligned16(a.x) && (OP == kLseFwd || OP == kLossFwd || aligned16(a.out)) &&
                      (OP != kSoftmaxBwd || aligned16(a.g));
     const int64_t sms = sm_count();
 #define PAMK_ROWS(V, N, W)                                                                              \
@@ -242,12 +318,13 @@ int max_grid(int64_t n) {
     return (int)(want < 1 ? 1 : (want < cap ? want : cap));
 }
 
-int run_rows(int op, bool approx, const float* x, const float* g, float* out, int64_t rows, int64_t len,
-             float offset, void* workspace, size_t workspace_bytes, void* stream) {
+int run_rows(int op, bool approx, RowArgs a, int64_t len, float offset, void* workspace, size_t workspace_bytes, void* stream) {
+    const int64_t rows = a.rows;
     if (rows < 0 || len <= 0) return PAMK_ERR_ARG;
     if (len > kMaxLen) return PAMK_ERR_SIZE;
     if (rows == 0) return PAMK_OK;
-    if (!x || !out || ((op == kSoftmaxBwd || op == kLseBwd) && !g)) return PAMK_ERR_ARG;
+    if (!a.x || !a.out || ((op == kSoftmaxBwd || op == kLseBwd || op == kCeBwd) && !a.g)) return PAMK_ERR_ARG;
+    if ((op == kLossFwd || op == kLossBwd || op == kCeBwd) && !a.target) return PAMK_ERR_ARG;
     const int64_t n = rows * len;
     const int grid = max_grid(n);
     if (!workspace || workspace_bytes < (size_t)grid * sizeof(float) || (reinterpret_cast<uintptr_t>(workspace) & 15u))
@@ -255,16 +332,28 @@ int run_rows(int op, bool approx, const float* x, const float* g, float* out, in
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int32_t off = offset_bits(offset);
     float* partials = static_cast<float*>(workspace);
-    scaled_max_kernel<<<grid, 256, 0, st>>>(x, n, off, partials);
+    scaled_max_kernel<<<grid, 256, 0, st>>>(a.x, n, off, partials);
     int rc = check_launch();
     if (rc != PAMK_OK) return rc;
-    const RowArgs a{x, g, out, partials, grid, rows, (int)len, off};
+    a.partials = partials;
+    a.partial_count = grid;
+    a.len = (int)len;
+    a.off = off;
     switch (op) {
         case kSoftmaxFwd: return launch_rows<kSoftmaxFwd, false>(a, st);
         case kLseFwd: return launch_rows<kLseFwd, false>(a, st);
+        case kLossFwd: return launch_rows<kLossFwd, false>(a, st);
+        case kCeBwd: return launch_rows<kCeBwd, false>(a, st);
         case kSoftmaxBwd: return approx ? launch_rows<kSoftmaxBwd, true>(a, st) : launch_rows<kSoftmaxBwd, false>(a, st);
+        case kLossBwd: return approx ? launch_rows<kLossBwd, true>(a, st) : launch_rows<kLossBwd, false>(a, st);
         default: return approx ? launch_rows<kLseBwd, true>(a, st) : launch_rows<kLseBwd, false>(a, st);
     }
+}
+
+RowArgs plain_rows(const float* x, const float* g, float* out, int64_t rows) {
+    RowArgs a{};
+    a.x = x; a.g = g; a.out = out; a.rows = rows;
+    return a;
 }
 
 }  // namespace
@@ -283,22 +372,49 @@ size_t pamk_softmax_workspace_bytes(int64_t rows, int64_t len) {
 
 int pamk_softmax_fwd(const float* x, float* y, int64_t rows, int64_t len, float offset,
                      void* workspace, size_t workspace_bytes, void* stream) {
-    return run_rows(kSoftmaxFwd, false, x, nullptr, y, rows, len, offset, workspace, workspace_bytes, stream);
+    return run_rows(kSoftmaxFwd, false, plain_rows(x, nullptr, y, rows), len, offset, workspace, workspace_bytes, stream);
 }
 
 int pamk_softmax_bwd(const float* x, const float* dy, float* dx, int64_t rows, int64_t len, float offset,
                      int approx_bwd, void* workspace, size_t workspace_bytes, void* stream) {
-    return run_rows(kSoftmaxBwd, approx_bwd != 0, x, dy, dx, rows, len, offset, workspace, workspace_bytes, stream);
+    return run_rows(kSoftmaxBwd, approx_bwd != 0, plain_rows(x, dy, dx, rows), len, offset, workspace, workspace_bytes, stream);
 }
 
 int pamk_logsumexp_fwd(const float* x, float* y, int64_t rows, int64_t len, float offset,
                        void* workspace, size_t workspace_bytes, void* stream) {
-    return run_rows(kLseFwd, false, x, nullptr, y, rows, len, offset, workspace, workspace_bytes, stream);
+    return run_rows(kLseFwd, false, plain_rows(x, nullptr, y, rows), len, offset, workspace, workspace_bytes, stream);
 }
 
 int pamk_logsumexp_bwd(const float* x, const float* dy, float* dx, int64_t rows, int64_t len, float offset,
                        int approx_bwd, void* workspace, size_t workspace_bytes, void* stream) {
-    return run_rows(kLseBwd, approx_bwd != 0, x, dy, dx, rows, len, offset, workspace, workspace_bytes, stream);
+    return run_rows(kLseBwd, approx_bwd != 0, plain_rows(x, dy, dx, rows), len, offset, workspace, workspace_bytes, stream);
+}
+
+int pamk_ls_loss_fwd(const float* logits, const long long* target, float* rows_out, int64_t rows, int64_t len,
+                     int has_ignore, long long ignore_index, float offset,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+    RowArgs a = plain_rows(logits, nullptr, rows_out, rows);
+    a.target = target; a.has_ignore = has_ignore; a.ignore = ignore_index;
+    return run_rows(kLossFwd, false, a, len, offset, workspace, workspace_bytes, stream);
+}
+
+int pamk_ls_loss_bwd(const float* logits, const long long* target, float* dlogits, int64_t rows, int64_t len,
+                     float d_nll, float d_smooth, int has_ignore, long long ignore_index, float offset, int approx_bwd,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+    RowArgs a = plain_rows(logits, nullptr, dlogits, rows);
+    a.target = target; a.has_ignore = has_ignore; a.ignore = ignore_index;
+    a.c0 = d_nll; a.c1 = d_smooth;
+    return run_rows(kLossBwd, approx_bwd != 0, a, len, offset, workspace, workspace_bytes, stream);
+}
+
+int pamk_cross_entropy_bwd(const float* logits, const long long* target, const float* class_weight, const float* grad_out,
+                           float* dlogits, int64_t rows, int64_t len, float hot_prob, float cold_prob, float mean_rows,
+                           int has_ignore, long long ignore_index, float offset,
+                           void* workspace, size_t workspace_bytes, void* stream) {
+    RowArgs a = plain_rows(logits, grad_out, dlogits, rows);
+    a.target = target; a.weight = class_weight; a.has_ignore = has_ignore; a.ignore = ignore_index;
+    a.c0 = hot_prob; a.c1 = cold_prob; a.c2 = mean_rows;
+    return run_rows(kCeBwd, false, a, len, offset, workspace, workspace_bytes, stream);
 }
 
 }

@@ -179,3 +179,64 @@ def test_function_dictionaries_on_cuda(factories):
     assert_bits_equal(pam_ops["bmm"](a, b), pam.bmm(a, b, approx_bwd=True), "dictionary bmm")
     assert_bits_equal(pam_ops["softmax"](a, dim=-1, dtype=torch.float32), pam.softmax(a, dim=-1, approx_bwd=True),
                       "dictionary softmax (unknown keyword arguments are dropped)")
+
+
+@pytest.mark.parametrize("name", ["deit", "transformer"])
+def test_full_models_built_by_the_factories_equal_the_functional_graphs(factories, name):
+    """DeiT-tiny (12 blocks, d 192, 197 tokens) and the 6+6 transformer (d 512, vocabulary 10000) as
+    modules built from the forks' configuration strings (pam_b200/models.py) against the functional
+    graphs of pam_b200/steps.py — the form the oracle comparisons of test_gpu_steps.py use — with the
+    same weights and batch: loss and every gradient bit for bit."""
+    import pam_b200 as pam
+    from pam_b200 import models, steps
+    dev = torch.device("cuda", 0)
+    cfgs = models.pam_cfgs(approx_bwd=True)
+    g = torch.Generator().manual_seed(77)
+    if name == "deit":
+        cfg = steps.DeitConfig()
+        params = steps.deit_params(cfg, g)
+        images = torch.randn(2, cfg.channels, cfg.image, cfg.image, generator=g).to(dev)
+        labels = torch.randint(0, cfg.classes, (2,), generator=g).to(dev)
+        model = models.VisionTransformer(cfg, linear_cfg=cfgs["linear"], conv_cfg=cfgs["linear"], norm_cfg=cfgs["norm"],
+                                         functional_cfg=cfgs["function"]).load_parameters(params).to(dev)
+        got = torch.nn.functional.cross_entropy(model(images), labels)
+        leaves = steps.to_device(params, dev)
+        want = steps.deit_loss(pam, leaves, images, labels, cfg, KW)
+        flat_of = {"patch_embed.proj.weight": "patch.w", "patch_embed.proj.bias": "patch.b", "cls_token": "cls", "pos_embed": "pos",
+                   "norm.weight": "norm.w", "norm.bias": "norm.b", "head.weight": "head.w", "head.bias": "head.b"}
+        stems = {"norm1": "ln1", "attn.qkv": "qkv", "attn.proj": "proj", "norm2": "ln2", "mlp.fc1": "fc1", "mlp.fc2": "fc2"}
+        for i in range(cfg.depth):
+            for dotted, stem in stems.items():
+                flat_of[f"blocks.{i}.{dotted}.weight"] = f"blocks.{i}.{stem}.w"
+                flat_of[f"blocks.{i}.{dotted}.bias"] = f"blocks.{i}.{stem}.b"
+    else:
+        cfg = steps.TransformerConfig()
+        params = steps.transformer_params(cfg, g)
+        src, prev_out, target = (t.to(dev) for t in steps.transformer_batch(cfg, g, sentences=2, length=32))
+        model = models.Transformer(cfg, linear_cfg=cfgs["linear"], norm_cfg=cfgs["norm"], functional_cfg=cfgs["function"],
+                                   loss_functional_cfg=cfgs["function"]).load_parameters(params).to(dev)
+        got = model.loss(src, prev_out, target)
+        leaves = steps.to_device(params, dev)
+        want = steps.transformer_loss(pam, leaves, src, prev_out, target, cfg, KW)
+        flat_of = {"encoder.embed_tokens.weight": "enc.embed", "decoder.embed_tokens.weight": "dec.embed"}
+        attn = {"q_proj": "q", "k_proj": "k", "v_proj": "v", "out_proj": "out"}
+        for side, short, layers in (("encoder", "enc", cfg.encoder_layers), ("decoder", "dec", cfg.decoder_layers)):
+            for i in range(layers):
+                for kind, suffix in (("weight", "w"), ("bias", "b")):
+                    for dotted, a in attn.items():
+                        flat_of[f"{side}.layers.{i}.self_attn.{dotted}.{kind}"] = f"{short}.{i}.self.{a}.{suffix}"
+                        if side == "decoder":
+                            flat_of[f"{side}.layers.{i}.encoder_attn.{dotted}.{kind}"] = f"{short}.{i}.cross.{a}.{suffix}"
+                    flat_of[f"{side}.layers.{i}.self_attn_layer_norm.{kind}"] = f"{short}.{i}.ln_self.{suffix}"
+                    if side == "decoder":
+                        flat_of[f"{side}.layers.{i}.encoder_attn_layer_norm.{kind}"] = f"{short}.{i}.ln_cross.{suffix}"
+                    flat_of[f"{side}.layers.{i}.final_layer_norm.{kind}"] = f"{short}.{i}.ln_ffn.{suffix}"
+                    flat_of[f"{side}.layers.{i}.fc1.{kind}"] = f"{short}.{i}.fc1.{suffix}"
+                    flat_of[f"{side}.layers.{i}.fc2.{kind}"] = f"{short}.{i}.fc2.{suffix}"
+    got.backward()
+    want.backward()
+    assert_bits_equal(got.detach().reshape(1), want.detach().reshape(1), "loss")
+    named = dict(model.named_parameters())                   # (the tied output projection appears once)
+    assert set(named) == set(flat_of), sorted(set(named) ^ set(flat_of))
+    for dotted, flat in flat_of.items():
+        assert_bits_equal(named[dotted].grad.reshape(leaves[flat].shape), leaves[flat].grad, f"gradient of {dotted}")
