@@ -576,7 +576,7 @@ def training_step(args, case, rank, world, dev, steps, warmup):
                                    loss_functional_cfg=cfgs["function"])
         model.load_parameters(workloads.transformer_params(cfg, torch.Generator().manual_seed(5))).to(dev)
         host = tuple(t.pin_memory() for t in workloads.transformer_batch(cfg, g))
-        loss_fn = model.loss
+        loss_fn = lambda src, prev, tgt: model.loss(src, prev, tgt, fused=True)
         macs, hyper = 3 * workloads.transformer_macs(cfg), dict(lr=5e-4, betas=(0.9, 0.98), eps=1e-8, weight_decay=1e-4)
         what = "configs[2]: 6+6 transformer step, 4096 tokens per GPU"
     params = model

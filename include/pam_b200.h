@@ -214,16 +214,17 @@ int pamk_logsumexp_bwd(const float* x, const float* dy, float* dx, int64_t rows,
  * label_smoothed_nll_loss (fairseq/criterions/label_smoothed_cross_entropy.py:36-54).
  *   forward:  rows_out[r] = { logsumexp(x_r), -lprobs[r, target_r], -(sum_j lprobs[r, j]) }  ([rows, 3]);
  *             the last two are 0 for rows whose target is ignore_index (when has_ignore);
- *   backward: dlogits for d(loss)/d(sum of the nll column) = d_nll and d(loss)/d(sum of the smooth
- *             column) = d_smooth: -(d_smooth) - (d_nll at the target) plus the logsumexp gradient chain.
+ *   backward: dlogits for grads = { d(loss)/d(sum of the nll column), d(loss)/d(sum of the smooth column) }
+ *             (two fp32 values on the device, so that no host read is needed): -(d smooth) - (d nll at the
+ *             target) plus the logsumexp gradient chain.
  * The scalar combination loss = pam(1 - eps - eps_i, nll) + pam(eps_i, smooth) stays with the caller.
  * logits [rows, len] contiguous, target [rows] int64, len <= pamk_softmax_max_len(); workspace as for
  * pamk_softmax_fwd. */
 int pamk_ls_loss_fwd(const float* logits, const long long* target, float* rows_out, int64_t rows, int64_t len,
                      int has_ignore, long long ignore_index, float offset,
                      void* workspace, size_t workspace_bytes, void* stream);
-int pamk_ls_loss_bwd(const float* logits, const long long* target, float* dlogits, int64_t rows, int64_t len,
-                     float d_nll, float d_smooth, int has_ignore, long long ignore_index, float offset, int approx_bwd,
+int pamk_ls_loss_bwd(const float* logits, const long long* target, const float* grads, float* dlogits,
+                     int64_t rows, int64_t len, int has_ignore, long long ignore_index, float offset, int approx_bwd,
                      void* workspace, size_t workspace_bytes, void* stream);
 /* Gradient of pam_opt.cross_entropy (pam/pam_opt.py:27-51) in one launch:
  *   d = pam_softmax(x) - target distribution (hot_prob at the target, cold_prob elsewhere);

@@ -56,7 +56,7 @@ _SIGNATURES = {
     "pamk_logsumexp_fwd": (_i, [_p, _p, _i64, _i64, _f, _p, _sz, _p]),
     "pamk_logsumexp_bwd": (_i, [_p, _p, _p, _i64, _i64, _f, _i, _p, _sz, _p]),
     "pamk_ls_loss_fwd": (_i, [_p, _p, _p, _i64, _i64, _i, ctypes.c_longlong, _f, _p, _sz, _p]),
-    "pamk_ls_loss_bwd": (_i, [_p, _p, _p, _i64, _i64, _f, _f, _i, ctypes.c_longlong, _f, _i, _p, _sz, _p]),
+    "pamk_ls_loss_bwd": (_i, [_p, _p, _p, _p, _i64, _i64, _i, ctypes.c_longlong, _f, _i, _p, _sz, _p]),
     "pamk_cross_entropy_bwd": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _f, _f, _f, _i, ctypes.c_longlong, _f, _p, _sz, _p]),
     "pamk_adam_step": (_i, [_p, _p, _p, _p, _p, _i] + [_f] * 8 + [_p]),
     "pamk_issue_rate": (_i, [_i, _i, _i, _p, ctypes.POINTER(_f), ctypes.POINTER(ctypes.c_double), _p]),

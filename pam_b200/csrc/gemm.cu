@@ -404,20 +404,35 @@ gemm_kernel(const GemmParams p) {
                         }
                 }
             } else {
-                // (one copy of each body: with the bodies unrolled together the loop measured a third slower)
-#pragma unroll 1
-                for (int kk = 0; kk < BK; ++kk) {
-                    PAMK_FRAGMENTS(kk)
-                    if (!((dirty >> kk) & 1u)) {
-#pragma unroll
-                        for (int i = 0; i < MT; ++i)
-#pragma unroll
-                            for (int j = 0; j < MT; ++j) acc[i][j] = fadd(acc[i][j], i2f(iadd(a[i], b[j])));
-                    } else {
+                // The lines are walked in runs of one kind, each run by a loop of its own with one copy of
+                // its body (with the three bodies side by side in one loop the schedule cost 12 %).
+                const unsigned flush = dirty & ~full & all_lines;
+                int kk = 0;
+                while (kk < BK) {
+                    const unsigned here = 1u << kk;
+                    if (full & here) {
+                        PAMK_FRAGMENTS(kk)
                         float araw[MT];
 #pragma unroll
                         for (int i = 0; i < MT; ++i) araw[i] = i2f(iadd(a[i], p.bias_sub));
-                        if (!((full >> kk) & 1u)) {
+#pragma unroll
+                        for (int i = 0; i < MT; ++i)
+#pragma unroll
+                            for (int j = 0; j < MT; ++j) {
+                                const float mag = fabsf(fmul(araw[i], i2f(b[j])));
+                                const float prod = mag <= i2f(kPassBits) ? i2f(iadd(a[i], b[j])) : quiet_nan();
+                                if (!(mag <= i2f(kFlushBits))) acc[i][j] = fadd(acc[i][j], prod);
+                            }
+                        ++kk;
+                    } else if (flush & here) {
+                        const unsigned others = ~flush >> kk;
+                        const int end = min(BK, kk + __ffs((int)others) - 1);
+#pragma unroll 1
+                        for (; kk < end; ++kk) {
+                            PAMK_FRAGMENTS(kk)
+                            float araw[MT];
+#pragma unroll
+                            for (int i = 0; i < MT; ++i) araw[i] = i2f(iadd(a[i], p.bias_sub));
 #pragma unroll
                             for (int i = 0; i < MT; ++i)
 #pragma unroll
@@ -425,15 +440,17 @@ gemm_kernel(const GemmParams p) {
                                     const float mag = fabsf(fmul(araw[i], i2f(b[j])));
                                     if (mag > i2f(kFlushBits)) acc[i][j] = fadd(acc[i][j], i2f(iadd(a[i], b[j])));
                                 }
-                        } else {
+                        }
+                    } else {
+                        const unsigned others = (dirty & all_lines) >> kk;
+                        const int end = others ? kk + __ffs((int)others) - 1 : BK;
+#pragma unroll 1
+                        for (; kk < end; ++kk) {
+                            PAMK_FRAGMENTS(kk)
 #pragma unroll
                             for (int i = 0; i < MT; ++i)
 #pragma unroll
-                                for (int j = 0; j < MT; ++j) {
-                                    const float mag = fabsf(fmul(araw[i], i2f(b[j])));
-                                    const float prod = mag <= i2f(kPassBits) ? i2f(iadd(a[i], b[j])) : quiet_nan();
-                                    if (!(mag <= i2f(kFlushBits))) acc[i][j] = fadd(acc[i][j], prod);
-                                }
+                                for (int j = 0; j < MT; ++j) acc[i][j] = fadd(acc[i][j], i2f(iadd(a[i], b[j])));
                         }
                     }
                 }

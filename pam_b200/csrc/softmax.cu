@@ -82,7 +82,7 @@ struct RowArgs {
     const float* weight;     // optional per-class weights (cross-entropy gradient)
     long long ignore;        // rows whose target equals this contribute nothing (when has_ignore)
     int has_ignore;
-    float c0, c1, c2;        // label-smoothed loss backward: d nll, d smooth; cross-entropy: hot / cold target probability, row count
+    float c0, c1, c2;        // cross-entropy gradient: hot / cold target probability, row count (0 = no mean)
 };
 
 // Thread t of a group of WARPS*32 threads holds NCH chunks of VEC consecutive columns: chunk q
@@ -215,7 +215,8 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
             // logsumexp gradient chain, and x receives both contributions
             const long long tgt = a.target[row];
             const bool ignored = a.has_ignore && tgt == a.ignore;
-            const float d_all = ignored ? 0.0f : -a.c1, d_hot = ignored ? 0.0f : fadd(-a.c0, -a.c1);
+            const float d_nll = __ldg(a.g), d_smooth = __ldg(a.g + 1);
+            const float d_all = ignored ? 0.0f : -d_smooth, d_hot = ignored ? 0.0f : fadd(-d_nll, -d_smooth);
             float part_d = 0.0f;
 #pragma unroll
             for (int i = 0; i < NCH * VEC; ++i) {
@@ -323,7 +324,7 @@ int run_rows(int op, bool approx, RowArgs a, int64_t len, float offset, void* wo
     if (rows < 0 || len <= 0) return PAMK_ERR_ARG;
     if (len > kMaxLen) return PAMK_ERR_SIZE;
     if (rows == 0) return PAMK_OK;
-    if (!a.x || !a.out || ((op == kSoftmaxBwd || op == kLseBwd || op == kCeBwd) && !a.g)) return PAMK_ERR_ARG;
+    if (!a.x || !a.out || ((op == kSoftmaxBwd || op == kLseBwd || op == kCeBwd || op == kLossBwd) && !a.g)) return PAMK_ERR_ARG;
     if ((op == kLossFwd || op == kLossBwd || op == kCeBwd) && !a.target) return PAMK_ERR_ARG;
     const int64_t n = rows * len;
     const int grid = max_grid(n);
@@ -398,12 +399,11 @@ int pamk_ls_loss_fwd(const float* logits, const long long* target, float* rows_o
     return run_rows(kLossFwd, false, a, len, offset, workspace, workspace_bytes, stream);
 }
 
-int pamk_ls_loss_bwd(const float* logits, const long long* target, float* dlogits, int64_t rows, int64_t len,
-                     float d_nll, float d_smooth, int has_ignore, long long ignore_index, float offset, int approx_bwd,
+int pamk_ls_loss_bwd(const float* logits, const long long* target, const float* grads, float* dlogits,
+                     int64_t rows, int64_t len, int has_ignore, long long ignore_index, float offset, int approx_bwd,
                      void* workspace, size_t workspace_bytes, void* stream) {
-    RowArgs a = plain_rows(logits, nullptr, dlogits, rows);
+    RowArgs a = plain_rows(logits, grads, dlogits, rows);
     a.target = target; a.has_ignore = has_ignore; a.ignore = ignore_index;
-    a.c0 = d_nll; a.c1 = d_smooth;
     return run_rows(kLossBwd, approx_bwd != 0, a, len, offset, workspace, workspace_bytes, stream);
 }
 

@@ -219,5 +219,10 @@ def get_function_dict(desc):
     defaults, overrides = desc.get("dkwargs", {}), desc.get("okwargs", {})
     # as in the reference (factories.py:291-298) the dict form wraps the full PAM dictionary
     # whatever `type` says
-    return {name: (lambda *a, _f=func, **ka: call_valid_kwargs(_f, {**defaults, **ka, **overrides}, a))
-            for name, func in _pam_dict().items()}
+    def bind(func):
+        def bound(*a, **ka):
+            return call_valid_kwargs(func, {**defaults, **ka, **overrides}, a)
+        # what the wrapper binds, for callers that can fuse a chain of these operators into one kernel
+        bound.pam_function, bound.pam_kwargs = func, {**defaults, **overrides}
+        return bound
+    return {name: bind(func) for name, func in _pam_dict().items()}

@@ -172,6 +172,76 @@ def logsumexp(x, dim, keepdim=False, *, offset=None, approx_bwd=False):
     return out.unsqueeze(-1) if keepdim else out
 
 
+# ---- loss kernels ---------------------------------------------------------------------------------------
+
+def loss_supported(logits, target):
+    return (enabled and isinstance(logits, torch.Tensor) and logits.is_cuda and logits.dtype == torch.float32 and
+            logits.dim() == 2 and 0 < logits.shape[-1] <= _MAX_ROW and logits.shape[0] > 0 and
+            isinstance(target, torch.Tensor) and target.device == logits.device and target.dtype == torch.int64 and
+            target.numel() == logits.shape[0])
+
+
+def _loss_call(name, logits, args):
+    dev = logits.device
+    handle = _lib.lib()
+    rows, length = logits.shape
+    ws_bytes = handle.pamk_softmax_workspace_bytes(rows, length)
+    ws = _workspace(dev, ws_bytes)
+    with _lib.device_guard(dev):
+        status = getattr(handle, name)(*args, ws.data_ptr(), ws_bytes, _lib.stream_ptr(dev))
+    _lib.check(status, name)
+
+
+class _LabelSmoothedSums(torch.autograd.Function):
+    """(sum of -lprobs[target], sum of -lprobs over all classes) of the PAM log-softmax of `logits`,
+    from the logits in one row pass; rows whose target is `ignore_index` contribute nothing."""
+
+    @staticmethod
+    def forward(ctx, logits, target, ignore_index, offset, approx):
+        x2 = logits.contiguous()
+        tgt = target.reshape(-1).contiguous()
+        rows, length = x2.shape
+        out = torch.empty(rows, 3, dtype=torch.float32, device=x2.device)
+        has_ignore = ignore_index is not None
+        _loss_call("pamk_ls_loss_fwd", x2, [x2.data_ptr(), tgt.data_ptr(), out.data_ptr(), rows, length,
+                                            int(has_ignore), int(ignore_index or 0), offset])
+        ctx.save_for_backward(x2, tgt)
+        ctx.cfg = (ignore_index, offset, approx)
+        return out[:, 1].sum(), out[:, 2].sum()
+
+    @staticmethod
+    def backward(ctx, g_nll, g_smooth):
+        x2, tgt = ctx.saved_tensors
+        ignore_index, offset, approx = ctx.cfg
+        rows, length = x2.shape
+        grads = torch.stack([g_nll.reshape(()).float(), g_smooth.reshape(()).float()]).contiguous()
+        dx = torch.empty_like(x2)
+        has_ignore = ignore_index is not None
+        _loss_call("pamk_ls_loss_bwd", x2, [x2.data_ptr(), tgt.data_ptr(), grads.data_ptr(), dx.data_ptr(), rows, length,
+                                            int(has_ignore), int(ignore_index or 0), offset, int(bool(approx))])
+        return dx, None, None, None, None
+
+
+def label_smoothed_sums(logits, target, ignore_index=None, *, offset=None, approx_bwd=False):
+    return _LabelSmoothedSums.apply(logits, target, ignore_index, _offset(offset), _flag(approx_bwd))
+
+
+def cross_entropy_grad(logits, target, weight, grad_out, *, hot, cold, mean_rows, ignore_index=None, offset=None):
+    """The gradient of pam_opt.cross_entropy with respect to the logits in one launch (see
+    pamk_cross_entropy_bwd in the C header); `grad_out` is the incoming 0-d gradient tensor."""
+    x2 = logits.contiguous()
+    tgt = target.reshape(-1).contiguous()
+    rows, length = x2.shape
+    dx = torch.empty_like(x2)
+    w = None if weight is None else weight.detach().float().contiguous()
+    g = grad_out.detach().reshape(1).float().contiguous()
+    has_ignore = ignore_index is not None
+    _loss_call("pamk_cross_entropy_bwd", x2, [x2.data_ptr(), tgt.data_ptr(), None if w is None else w.data_ptr(), g.data_ptr(),
+                                              dx.data_ptr(), rows, length, float(hot), float(cold), float(mean_rows),
+                                              int(has_ignore), int(ignore_index or 0), _offset(offset)])
+    return dx
+
+
 # ---- linear layer with bias ----------------------------------------------------------------------------
 
 def linear_bias_supported(X2, W, bias):

@@ -217,9 +217,15 @@ class Transformer(nn.Module):
             y = layer(y, x, future)
         return self.decoder.output_projection(y)
 
-    def loss(self, src, prev_out, target):
-        """Label-smoothed negative log-likelihood summed over the target tokens."""
+    def loss(self, src, prev_out, target, fused=False):
+        """Label-smoothed negative log-likelihood summed over the target tokens.  `fused` takes the
+        loss from the logits in one row kernel each way (pam_opt.label_smoothed_nll_loss): the same
+        values up to the association of the row sums."""
         ops, cfg = self.loss_ops, self.cfg
+        if fused:
+            from . import pam_opt
+            logits = self(src, prev_out).reshape(-1, cfg.vocab)
+            return pam_opt.label_smoothed_nll_loss(logits, target.reshape(-1), cfg.label_smoothing, op_dict=ops)[0]
         lprobs = ops["log_softmax"](self(src, prev_out).reshape(-1, cfg.vocab), dim=-1)
         nll = -lprobs.gather(-1, target.reshape(-1, 1)).sum()
         smooth = -lprobs.sum()
