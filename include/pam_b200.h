@@ -115,6 +115,23 @@ int pamk_matmul_bias(int mul_kind, const float* A, const float* B, const float* 
                      int64_t sAb, int64_t sAm, int64_t sAk,
                      int64_t sBb, int64_t sBk, int64_t sBn,
                      float offset, int split_k, void* workspace, size_t workspace_bytes, void* stream);
+/* PAM product over a two-level batch with strided operands and a strided output, for attention
+ * products that read q, k, v straight out of the fused projection's output and write the context
+ * back in token-major layout (timm vision_transformer.py:72-93 folds and copies these with
+ * flatten / transpose / reshape before and after pam.bmm).  Batch z = o * batch_inner + i:
+ *   C[o*sCo + i*sCi + m*sCm + n] = sum_k pam(A[o*sAo + i*sAi + m*sAm + k*sAk], B[o*sBo + i*sBi + k*sBk + n*sBn])
+ * with the columns of C contiguous (sCm >= N).  Each operand needs sAm == 1 or sAk == 1 (sBn or sBk)
+ * as for pamk_matmul.  has_post_scale != 0: every finished sum is PAM-multiplied by post_scale
+ * (the `* self.scale` after the score product, as the operator dictionary's mul does it) before it
+ * is stored.  Products, order of summation and the choice of split_k = 0 are those of pamk_matmul
+ * on the same shapes, so the values equal the copy-then-bmm route bit for bit. */
+int pamk_matmul_strided(const float* A, const float* B, float* C,
+                        int64_t batch_outer, int64_t batch_inner, int64_t M, int64_t N, int64_t K,
+                        int64_t sAo, int64_t sAi, int64_t sAm, int64_t sAk,
+                        int64_t sBo, int64_t sBi, int64_t sBk, int64_t sBn,
+                        int64_t sCo, int64_t sCi, int64_t sCm,
+                        float offset, int has_post_scale, float post_scale,
+                        int split_k, void* workspace, size_t workspace_bytes, void* stream);
 /* Scratch needed by pamk_matmul for a given split_k (0 for split_k <= 1). */
 size_t pamk_matmul_workspace_bytes(int64_t batch, int64_t M, int64_t N, int split_k);
 /* The split the library would choose for split_k = 0 given unlimited workspace. */
@@ -203,6 +220,11 @@ int pamk_softmax_fwd(const float* x, float* y, int64_t rows, int64_t len, float 
                      void* workspace, size_t workspace_bytes, void* stream);
 int pamk_softmax_bwd(const float* x, const float* dy, float* dx, int64_t rows, int64_t len, float offset,
                      int approx_bwd, void* workspace, size_t workspace_bytes, void* stream);
+/* pamk_softmax_bwd followed by a PAM multiplication of dx by post_scale, in the same pass: the
+ * gradient of softmax(pam(scores, scale)) with respect to the scores when the scaling's backward
+ * is the approximate form pam(d, scale) (pam/cuda_bindings.py:39-50 with approx_bwd). */
+int pamk_softmax_bwd_scaled(const float* x, const float* dy, float* dx, int64_t rows, int64_t len, float offset,
+                            int approx_bwd, float post_scale, void* workspace, size_t workspace_bytes, void* stream);
 int pamk_logsumexp_fwd(const float* x, float* y, int64_t rows, int64_t len, float offset,
                        void* workspace, size_t workspace_bytes, void* stream);
 int pamk_logsumexp_bwd(const float* x, const float* dy, float* dx, int64_t rows, int64_t len, float offset,

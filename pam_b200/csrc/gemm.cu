@@ -38,19 +38,29 @@ namespace {
 
 enum Mode { kPam = 0, kStd = 1, kBwdL = 2, kBwdR = 3 };
 
-// One matrix operand: element (r, k) of batch z lives at p[z*sb + r*sr + k*sk], where r is the
-// non-contracted index (row of A / column of B).
+// One matrix operand: element (r, k) of batch z lives at p[(z / inner)*sb + z*sb2 + r*sr + k*sk], where r
+// is the non-contracted index (row of A / column of B) and `inner` (GemmParams) is the size of the inner
+// batch dimension (1 for a plain batch: the heads of an attention product otherwise).  run() derives
+// this form from the caller's (outer stride, inner stride): sb = outer - inner * inner_stride,
+// sb2 = inner_stride; with inner = 1, sb = 0 and sb2 = the batch stride.
 struct MatArg {
     const float* p;
     int64_t sb, sr, sk;
+    int64_t sb2;
 };
 
 struct GemmParams {
     MatArg A, B;
     const float* D;           // exact-gradient product only: the operand the slope depends on
     int64_t sDb, sDm, sDn;
-    float* C;                 // [batch][M][N], or [split][batch][M][N] partials when splits > 1
+    float* C;                 // output, or [split][batch][M][N] partials when splits > 1
+    int64_t ldc, sCb, sCb2;   // output row stride and batch strides (outer, inner); columns are contiguous
+    int64_t sCsplit;          // distance between the partials of two K ranges
     const float* bias;        // optional [N]: added (ordinary fp32 add) to every output row after its sum
+    int post;                 // multiply every finished sum by post_scale (PAM product) before it is stored
+    float post_scale;
+    int inner;                // size of the inner batch dimension (>= 1)
+    unsigned inner_magic;     // floor(2^32 / inner) + 1 (0 when inner = 1): z / inner = umulhi(z, inner_magic)
     int M, N, K, batch;
     int splits, k_chunk;      // K is cut into `splits` ranges of k_chunk (a multiple of the slab)
     int32_t bias_sub;         // 0x3f800000 - offset_bits
@@ -260,8 +270,12 @@ gemm_kernel(const GemmParams p) {
     const int k_end = min(p.K, k_begin + p.k_chunk);
     const int slabs = (k_end - k_begin + BK - 1) / BK;
 
-    const float* Ab = p.A.p + (int64_t)z * p.A.sb;
-    const float* Bb = p.B.p + (int64_t)z * p.B.sb;
+    // batch z = outer * inner + (index in the inner dimension); outer = z / inner by a multiply-high with
+    // the reciprocal prepared on the host (exact for z < 65536, the grid limit); the strides arrive
+    // rearranged so that the offset is outer * sb + z * sb2
+    const unsigned zo = __umulhi((unsigned)z, p.inner_magic);
+    const float* Ab = p.A.p + (int64_t)zo * p.A.sb + (int64_t)z * p.A.sb2;
+    const float* Bb = p.B.p + (int64_t)zo * p.B.sb + (int64_t)z * p.B.sb2;
 
     float acc[MT][MT];
 #pragma unroll
@@ -485,8 +499,9 @@ gemm_kernel(const GemmParams p) {
     for (int s = 0; s < slabs; ++s) slab_iteration(s);
 
     // ---- epilogue ----------------------------------------------------------------------------
-    float* Cz = p.C + ((int64_t)sp * p.batch + z) * ((int64_t)p.M * p.N);
-    const bool vec_out = (p.N & 3) == 0 && aligned16(p.C);
+    float* Cz = p.C + (int64_t)sp * p.sCsplit + (int64_t)__umulhi((unsigned)z, p.inner_magic) * p.sCb + (int64_t)z * p.sCb2;
+    const bool vec_out = ((p.N | p.ldc | p.sCb | p.sCb2 | p.sCsplit) & 3) == 0 && aligned16(p.C);
+    const bool post = p.post != 0 && p.splits == 1;             // (with split-K the reduction pass applies it)
     const bool add_bias = p.bias != nullptr && p.splits == 1;   // (with split-K the reduction pass adds it)
     if constexpr (MODE != kPam) {
         // The reference walks K in zero-filled tiles of 32 (cuda_kernels.cu:526-571, 608-629): when K
@@ -509,7 +524,7 @@ gemm_kernel(const GemmParams p) {
     for (int i = 0; i < MT; ++i) {
         const int row = m0 + ty * 4 + (i & 3) + (i >> 2) * (BM / 2);
         if (row >= p.M) continue;
-        float* crow = Cz + (int64_t)row * p.N;
+        float* crow = Cz + (int64_t)row * p.ldc;
 #pragma unroll
         for (int h = 0; h < MT / 4; ++h) {
             const int col = n0 + tx * 4 + h * (BN / 2);
@@ -517,6 +532,10 @@ gemm_kernel(const GemmParams p) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
                     if (col + j < p.N) acc[i][h * 4 + j] = fadd(acc[i][h * 4 + j], __ldg(p.bias + col + j));
+            }
+            if (post) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][h * 4 + j] = mul(acc[i][h * 4 + j], p.post_scale, p.off);
             }
             if (vec_out) {
                 if (col < p.N)
@@ -531,16 +550,37 @@ gemm_kernel(const GemmParams p) {
     }
 }
 
-// Adds the split-K partials in split order: C = ((P0 + P1) + P2) + ... (+ bias[column] last)
-__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, float* __restrict__ C,
+// Where the finished sums of a split-K product go: a plain [batch][M][N] array, or the strided output
+// of the call (row stride and two batch strides).
+struct OutArg {
+    float* C;
+    int64_t ldc, sCb, sCb2;
+    int M, N, inner;
+    int contiguous;
+};
+
+// Adds the split-K partials in split order: C = ((P0 + P1) + P2) + ... (+ bias[column] last; then the
+// PAM product with post_scale, if asked for)
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, const OutArg o,
                                                             int64_t count, int splits,
-                                                            const float* __restrict__ bias, int N) {
+                                                            const float* __restrict__ bias, int post,
+                                                            float post_scale, int32_t off) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
         float v = part[i];
         for (int s = 1; s < splits; ++s) v = fadd(v, part[(int64_t)s * count + i]);
-        if (bias != nullptr) v = fadd(v, __ldg(bias + (int)(i % N)));
-        C[i] = v;
+        if (bias != nullptr) v = fadd(v, __ldg(bias + (int)(i % o.N)));
+        if (post) v = mul(v, post_scale, off);
+        if (o.contiguous) {
+            o.C[i] = v;
+        } else {
+            const int64_t r = i / o.N;
+            const int col = (int)(i - r * o.N);
+            const int64_t z = r / o.M;
+            const int row = (int)(r - z * o.M);
+            const int64_t zo = z / o.inner;
+            o.C[zo * o.sCb + (z - zo * o.inner) * o.sCb2 + (int64_t)row * o.ldc + col] = v;
+        }
     }
 }
 
@@ -561,7 +601,7 @@ int dispatch(const GemmParams& p, bool a_kc, bool b_kc, bool vec, dim3 grid, cud
 // An operand can use 128-bit loads when its base and both non-unit strides keep every group of
 // four elements 16-byte aligned and its contiguous extent is a multiple of four.
 bool vectorisable(const MatArg& m, bool kc, int rows, int K) {
-    if (!aligned16(m.p) || (m.sb & 3)) return false;
+    if (!aligned16(m.p) || (m.sb & 3) || (m.sb2 & 3)) return false;   // (either form of the batch strides)
     return kc ? ((m.sr & 3) == 0 && (K & 3) == 0) : ((m.sk & 3) == 0 && (rows & 3) == 0);
 }
 
@@ -655,7 +695,7 @@ int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspa
         cudaStream_t st) {
     if (p.M == 0 || p.N == 0 || p.batch == 0) return PAMK_OK;
     const int64_t count = (int64_t)p.batch * p.M * p.N;
-    if (p.K == 0 && p.bias == nullptr) {
+    if (p.K == 0 && p.bias == nullptr && p.ldc == 0) {
         const cudaError_t e = cudaMemsetAsync(p.C, 0, count * sizeof(float), st);
         return e == cudaSuccess ? PAMK_OK : record_cuda_error(e);
     }
@@ -675,8 +715,31 @@ int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspa
     const int bm = pl.tile == kTileTiny ? TileTiny::BM : (pl.tile == kTileSmall ? TileSmall::BM : TileLarge::BM);
     const int bn = pl.tile == kTileTiny ? TileTiny::BN : (pl.tile == kTileSmall ? TileSmall::BN : TileLarge::BN);
     const int bk = pl.tile == kTileTiny ? TileTiny::BK : (pl.tile == kTileSmall ? TileSmall::BK : TileLarge::BK);
-    float* out = p.C;
-    if (pl.splits > 1) p.C = static_cast<float*>(workspace);
+    if (p.inner < 1) p.inner = 1;
+    if (p.ldc == 0) {                                        // plain output: [batch][M][N]
+        p.ldc = p.N;
+        p.sCb = (int64_t)p.inner * p.M * p.N;
+        p.sCb2 = (int64_t)p.M * p.N;
+    }
+    OutArg out{p.C, p.ldc, p.sCb, p.sCb2, p.M, p.N, p.inner,
+               p.ldc == p.N && p.sCb2 == (int64_t)p.M * p.N && p.sCb == (int64_t)p.inner * p.M * p.N};
+    if (pl.splits > 1) {                                     // partials: [split][batch][M][N] in the scratch
+        p.C = static_cast<float*>(workspace);
+        p.ldc = p.N;
+        p.sCb = (int64_t)p.inner * p.M * p.N;
+        p.sCb2 = (int64_t)p.M * p.N;
+        p.sCsplit = count;
+    }
+    // batch strides into the kernel's form (see MatArg)
+    const bool vec = vectorisable(p.A, a_kc, p.M, p.K) && vectorisable(p.B, b_kc, p.N, p.K);
+    auto kernel_form = [&](int64_t& outer, int64_t& inner_stride) {
+        if (p.inner == 1) { inner_stride = outer; outer = 0; }
+        else outer -= (int64_t)p.inner * inner_stride;
+    };
+    kernel_form(p.A.sb, p.A.sb2);
+    kernel_form(p.B.sb, p.B.sb2);
+    kernel_form(p.sCb, p.sCb2);
+    p.inner_magic = p.inner == 1 ? 0u : (unsigned)((uint64_t(1) << 32) / (uint64_t)p.inner) + 1u;
     const int slabs_total = (p.K + bk - 1) / bk;
     p.splits = pl.splits;
     p.k_chunk = ((slabs_total + pl.splits - 1) / pl.splits) * bk;
@@ -684,7 +747,6 @@ int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspa
     const int64_t gx = (p.N + bn - 1) / bn, gy = (p.M + bm - 1) / bm, gz = (int64_t)p.batch * pl.splits;
     if (gy > 65535 || gz > 65535) return PAMK_ERR_SIZE;
     const dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)gz);
-    const bool vec = vectorisable(p.A, a_kc, p.M, p.K) && vectorisable(p.B, b_kc, p.N, p.K);
     int rc;
     switch (mode) {
         case kPam:
@@ -706,7 +768,7 @@ int run(int mode, GemmParams p, bool a_kc, bool b_kc, int split_k, void* workspa
     const int64_t blocks = (count + 255) / 256;
     const int64_t cap = (int64_t)sm_count() * 8;
     splitk_reduce_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, st>>>(
-        static_cast<const float*>(workspace), out, count, pl.splits, p.bias, p.N);
+        static_cast<const float*>(workspace), out, count, pl.splits, p.bias, p.post, p.post_scale, p.off);
     return check_launch();
 }
 
@@ -813,6 +875,41 @@ int pamk_matmul(int mul_kind, const float* A, const float* B, float* C,
                 float offset, int split_k, void* workspace, size_t workspace_bytes, void* stream) {
     return pamk_matmul_bias(mul_kind, A, B, nullptr, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, offset, split_k,
                             workspace, workspace_bytes, stream);
+}
+
+int pamk_matmul_strided(const float* A, const float* B, float* C,
+                        int64_t batch_outer, int64_t batch_inner, int64_t M, int64_t N, int64_t K,
+                        int64_t sAo, int64_t sAi, int64_t sAm, int64_t sAk,
+                        int64_t sBo, int64_t sBi, int64_t sBk, int64_t sBn,
+                        int64_t sCo, int64_t sCi, int64_t sCm,
+                        float offset, int has_post_scale, float post_scale,
+                        int split_k, void* workspace, size_t workspace_bytes, void* stream) {
+    if (batch_outer < 0 || batch_inner < 0) return PAMK_ERR_ARG;
+    if (batch_inner > 0 && batch_outer > (0x7fffffff - 256) / batch_inner) return PAMK_ERR_SIZE;
+    const int64_t batch = batch_outer * batch_inner;
+    if (!dims_ok(batch, M, N, K)) return M < 0 || N < 0 || K < 0 ? PAMK_ERR_ARG : PAMK_ERR_SIZE;
+    if (split_k < 0) return PAMK_ERR_ARG;
+    if (batch == 0 || M == 0 || N == 0) return PAMK_OK;
+    if (C == nullptr || sCm < N) return PAMK_ERR_ARG;
+    GemmParams p{};
+    bool a_kc = true, b_kc = true;
+    if (K > 0) {
+        int rc = operand_layout(A, sAm, sAk, (int)M, (int)K, &a_kc);
+        if (rc != PAMK_OK) return rc;
+        rc = operand_layout(B, sBn, sBk, (int)N, (int)K, &b_kc);
+        if (rc != PAMK_OK) return rc;
+    }
+    p.A = {A, sAo, sAm, sAk, sAi};
+    p.B = {B, sBo, sBn, sBk, sBi};
+    p.C = C;
+    p.ldc = sCm; p.sCb = sCo; p.sCb2 = sCi;
+    p.inner = (int)batch_inner;
+    p.post = has_post_scale != 0;
+    p.post_scale = post_scale;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
+    p.off = offset_bits(offset);
+    p.bias_sub = isub(kBias, p.off);
+    return run(kPam, p, a_kc, b_kc, split_k, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 size_t pamk_matmul_static_scratch_bytes(void) { return kStaticScratchFloats * sizeof(float); }

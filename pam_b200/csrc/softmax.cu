@@ -83,6 +83,8 @@ struct RowArgs {
     long long ignore;        // rows whose target equals this contribute nothing (when has_ignore)
     int has_ignore;
     float c0, c1, c2;        // cross-entropy gradient: hot / cold target probability, row count (0 = no mean)
+    int post;                // softmax backward: multiply dx by post_scale (PAM product) before it is stored,
+    float post_scale;        // the gradient of a PAM scaling of the scores by a constant (approx_bwd form)
 };
 
 // Thread t of a group of WARPS*32 threads holds NCH chunks of VEC consecutive columns: chunk q
@@ -265,6 +267,7 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
                                            : exp_base_bwd(adj, d_big, lb2, off);
                 const float d_s = masked ? 0.0f : d_adj;
                 g.v[i] = APPROX ? mul(d_s, kLog2e, off) : mul_bwd(x.v[i], kLog2e, d_s, off);
+                if (a.post) g.v[i] = mul(g.v[i], a.post_scale, off);
             }
             g.store(a.out + row * a.len, a.len, t);
         } else {
@@ -379,6 +382,13 @@ int pamk_softmax_fwd(const float* x, float* y, int64_t rows, int64_t len, float 
 int pamk_softmax_bwd(const float* x, const float* dy, float* dx, int64_t rows, int64_t len, float offset,
                      int approx_bwd, void* workspace, size_t workspace_bytes, void* stream) {
     return run_rows(kSoftmaxBwd, approx_bwd != 0, plain_rows(x, dy, dx, rows), len, offset, workspace, workspace_bytes, stream);
+}
+
+int pamk_softmax_bwd_scaled(const float* x, const float* dy, float* dx, int64_t rows, int64_t len, float offset,
+                            int approx_bwd, float post_scale, void* workspace, size_t workspace_bytes, void* stream) {
+    RowArgs a = plain_rows(x, dy, dx, rows);
+    a.post = 1; a.post_scale = post_scale;
+    return run_rows(kSoftmaxBwd, approx_bwd != 0, a, len, offset, workspace, workspace_bytes, stream);
 }
 
 int pamk_logsumexp_fwd(const float* x, float* y, int64_t rows, int64_t len, float offset,

@@ -172,6 +172,111 @@ def logsumexp(x, dim, keepdim=False, *, offset=None, approx_bwd=False):
     return out.unsqueeze(-1) if keepdim else out
 
 
+# ---- attention over a fused q/k/v projection ------------------------------------------------------------
+
+def attention_supported(qkv, num_heads, approx_bwd=False):
+    """The strided route below needs fp32 CUDA input [B, N, 3*C] with C divisible by the heads, rows that
+    the softmax kernel can hold, at most 65535 (batch, head) pairs and the approximate backward for every
+    operand (the exact-gradient products take the forward output as a third operand)."""
+    if not (enabled and isinstance(qkv, torch.Tensor) and qkv.is_cuda and qkv.dtype == torch.float32):
+        return False
+    if qkv.dim() != 3 or qkv.numel() == 0 or qkv.shape[-1] % (3 * num_heads):
+        return False
+    approx = (approx_bwd,) if isinstance(approx_bwd, bool) else tuple(approx_bwd)
+    return all(approx) and qkv.shape[1] <= _MAX_ROW and qkv.shape[0] * num_heads <= 65535
+
+
+def _strided_product(dev, a_ptr, b_ptr, c_ptr, outer, inner, M, N, K, sa, sb, sc, offset, post_scale=None):
+    """One pamk_matmul_strided call with the split the plain product of the same shape would get."""
+    handle = _lib.lib()
+    split = handle.pamk_matmul_auto_split(outer * inner, M, N, K)
+    ws_ptr, ws_bytes = None, 0
+    if split > 1:
+        ws_bytes = handle.pamk_matmul_workspace_bytes(outer * inner, M, N, split)
+        ws_ptr = _workspace(dev, ws_bytes).data_ptr()
+    with _lib.device_guard(dev):
+        status = handle.pamk_matmul_strided(a_ptr, b_ptr, c_ptr, outer, inner, M, N, K, *sa, *sb, *sc, offset,
+                                            int(post_scale is not None), float(post_scale or 0.0), split,
+                                            ws_ptr, ws_bytes, _lib.stream_ptr(dev))
+    _lib.check(status, "pamk_matmul_strided")
+
+
+class _AttentionQKV(torch.autograd.Function):
+    """softmax(pam(q k^T, scale)) v on the heads of a fused projection, reading q, k, v where the projection
+    wrote them ([B, N, 3, heads, head_dim]) and writing the context token-major ([B, N, C]): the products,
+    the PAM scaling (in the score product's epilogue), the softmax and every gradient product have the
+    shapes, split-K plans and arithmetic of the chain bmm -> mul -> softmax -> bmm on flattened copies
+    (timm vision_transformer.py:72-93 in the fork), so the values are the same bit for bit; what is left out
+    are the copies around them and the two passes of the scaling over the [B*heads, N, N] scores."""
+
+    @staticmethod
+    def forward(ctx, qkv, heads, scale, offset):
+        qkv = qkv.contiguous()
+        B, N, C3 = qkv.shape
+        C = C3 // 3
+        hd = C // heads
+        dev = qkv.device
+        base = qkv.data_ptr()
+        q_ptr, k_ptr, v_ptr = base, base + 4 * C, base + 8 * C
+        scores = torch.empty(B * heads, N, N, dtype=torch.float32, device=dev)
+        # scores = pam(q k^T, scale): q rows and k rows are 3C apart, heads hd apart
+        _strided_product(dev, q_ptr, k_ptr, scores.data_ptr(), B, heads, N, N, hd,
+                         (N * C3, hd, C3, 1), (N * C3, hd, 1, C3), (heads * N * N, N * N, N), offset, post_scale=scale)
+        probs = _rows(_lib.lib(), "pamk_softmax_fwd", scores.view(-1, N), [], torch.empty_like(scores).view(-1, N), offset)
+        out = torch.empty(B, N, C, dtype=torch.float32, device=dev)
+        # context[b, i, h, :] = probs[b, h, i, :] v[b, :, h, :]
+        _strided_product(dev, probs.data_ptr(), v_ptr, out.data_ptr(), B, heads, N, hd, N,
+                         (heads * N * N, N * N, N, 1), (N * C3, hd, C3, 1), (N * C, hd, C), offset)
+        ctx.save_for_backward(qkv, scores, probs)
+        ctx.cfg = (heads, scale, offset)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        qkv, scores, probs = ctx.saved_tensors
+        heads, scale, offset = ctx.cfg
+        B, N, C3 = qkv.shape
+        C = C3 // 3
+        hd = C // heads
+        dev = qkv.device
+        g = g.contiguous()
+        base = qkv.data_ptr()
+        q_ptr, k_ptr, v_ptr = base, base + 4 * C, base + 8 * C
+        dqkv = torch.empty_like(qkv)
+        dq_ptr, dv_ptr = dqkv.data_ptr(), dqkv.data_ptr() + 8 * C
+        s_probs, s_ctx = (heads * N * N, N * N, N, 1), (N * C, hd, C, 1)
+        # d probs = d context v^T
+        dprobs = torch.empty_like(scores)
+        _strided_product(dev, g.data_ptr(), v_ptr, dprobs.data_ptr(), B, heads, N, N, hd,
+                         s_ctx, (N * C3, hd, 1, C3), (heads * N * N, N * N, N), offset)
+        # d v = probs^T d context, written where v's gradient lives in d qkv
+        _strided_product(dev, probs.data_ptr(), g.data_ptr(), dv_ptr, B, heads, N, hd, N,
+                         (heads * N * N, N * N, 1, N), (N * C, hd, C, 1), (N * C3, hd, C3), offset)
+        # d scores = pam(softmax backward, scale)
+        dscores = torch.empty_like(scores).view(-1, N)
+        rows = dscores.shape[0]
+        handle = _lib.lib()
+        ws_bytes = handle.pamk_softmax_workspace_bytes(rows, N)
+        ws = _workspace(dev, ws_bytes)
+        with _lib.device_guard(dev):
+            status = handle.pamk_softmax_bwd_scaled(scores.data_ptr(), dprobs.data_ptr(), dscores.data_ptr(), rows, N,
+                                                    offset, 1, scale, ws.data_ptr(), ws_bytes, _lib.stream_ptr(dev))
+        _lib.check(status, "pamk_softmax_bwd_scaled")
+        # d q = d scores k
+        _strided_product(dev, dscores.data_ptr(), k_ptr, dq_ptr, B, heads, N, hd, N,
+                         s_probs, (N * C3, hd, C3, 1), (N * C3, hd, C3), offset)
+        # d (k^T) = q^T d scores as the chain computes it ([head_dim, N] per head), then into k's slot
+        dkt = torch.empty(B, heads, hd, N, dtype=torch.float32, device=dev)
+        _strided_product(dev, q_ptr, dscores.data_ptr(), dkt.data_ptr(), B, heads, hd, N, N,
+                         (N * C3, hd, 1, C3), (heads * N * N, N * N, N, 1), (heads * hd * N, hd * N, N), offset)
+        dqkv.view(B, N, 3, heads, hd)[:, :, 1].copy_(dkt.permute(0, 3, 1, 2))
+        return dqkv, None, None, None
+
+
+def attention_qkv(qkv, num_heads, scale, *, offset=None):
+    return _AttentionQKV.apply(qkv, int(num_heads), float(scale), _offset(offset))
+
+
 # ---- loss kernels ---------------------------------------------------------------------------------------
 
 def loss_supported(logits, target):

@@ -31,7 +31,8 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from . import factories
+from . import factories, fused
+from .pam_opt import _pam_binding
 from .steps import DeitConfig, TransformerConfig, sinusoidal_positions
 
 
@@ -46,7 +47,12 @@ class Attention(nn.Module):
 
     def forward(self, x):
         B, N, C = x.shape
-        qkv = self.qkv(x).reshape(B, N, 3, self.num_heads, C // self.num_heads).permute(2, 0, 3, 1, 4)
+        qkv = self.qkv(x)
+        bound = _pam_binding(self.ops, ("bmm", "softmax", "mul"))
+        if bound is not None and fused.attention_supported(qkv, self.num_heads, bound.get("approx_bwd", False)):
+            # the same products, scaling and softmax on strided views of qkv: no copies around them
+            return self.proj(fused.attention_qkv(qkv, self.num_heads, self.scale, offset=bound.get("offset")))
+        qkv = qkv.reshape(B, N, 3, self.num_heads, C // self.num_heads).permute(2, 0, 3, 1, 4)
         q, k, v = qkv.unbind(0)
         attn = self.ops["bmm"](q.flatten(0, 1), k.transpose(-2, -1).flatten(0, 1))
         attn = self.ops["softmax"](self.ops["mul"](attn, self.scale), dim=-1)
