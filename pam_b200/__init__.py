@@ -19,6 +19,7 @@ from . import cuda_bindings, native, pam_ops, pam_opt      # noqa: F401
 from .pam_ops import *                                     # noqa: F401,F403
 from .pam_opt import cross_entropy, cross_entropy_autograd  # noqa: F401
 from .cuda_bindings import set_strict_k_order, strict_k_order  # noqa: F401
+from ._lib import set_nvtx  # noqa: F401
 
 __version__ = "0.1.0"
 

@@ -5,11 +5,10 @@ exception is raised.  PyTorch only supplies device memory and the stream; every 
 runs in the library's own sm_100a kernels.
 """
 import ctypes
+import os
 import pathlib
 
 import torch
-
-import os
 
 _PKG = pathlib.Path(__file__).resolve().parent
 # PAM_B200_LIBRARY points at another build of the same library (A/B comparisons of kernel variants).
@@ -65,11 +64,49 @@ _SIGNATURES = {
 }
 
 _lib = None
+_traced = None
+_nvtx = os.environ.get("PAM_B200_NVTX", "") not in ("", "0")
+
+
+class _Traced:
+    """The library with every entry point that takes a stream wrapped in an NVTX range named after
+    it, so that a timeline shows which library call a kernel belongs to (the reference's forks mark
+    their steps with record_function scopes and emit_nvtx, fairseq_cli/train.py:569-571)."""
+
+    def __init__(self, handle):
+        self._handle = handle
+        self._wrapped = {}
+
+    def __getattr__(self, name):
+        fn = getattr(self._handle, name)
+        args = _SIGNATURES.get(name, (None, ()))[1]
+        if not args or args[-1] is not _p:                 # no stream argument: nothing is launched
+            return fn
+        wrapped = self._wrapped.get(name)
+        if wrapped is None:
+            def wrapped(*a, _fn=fn, _name=name):
+                torch.cuda.nvtx.range_push(_name)
+                try:
+                    return _fn(*a)
+                finally:
+                    torch.cuda.nvtx.range_pop()
+            self._wrapped[name] = wrapped
+        return wrapped
+
+
+def set_nvtx(on):
+    """Turns the NVTX ranges around the library's launches on or off (also: PAM_B200_NVTX=1)."""
+    global _nvtx
+    _nvtx = bool(on)
 
 
 def lib():
     """The loaded library; raises if it was never built (``python -m pam_b200.build``)."""
-    global _lib
+    global _lib, _traced
+    if _lib is not None and _nvtx:
+        if _traced is None:
+            _traced = _Traced(_lib)
+        return _traced
     if _lib is None:
         if not LIB_PATH.exists():
             raise RuntimeError(
@@ -80,7 +117,7 @@ def lib():
             fn = getattr(handle, name)
             fn.restype, fn.argtypes = res, args
         _lib = handle
-    return _lib
+    return lib() if _nvtx else _lib
 
 
 def exported_names():

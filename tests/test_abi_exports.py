@@ -40,3 +40,21 @@ def test_argument_checks_need_no_gpu():
     assert h.pamk_matmul(0, ptr, ptr, ptr, 1, 2**31, 4, 4, 0, 4, 1, 0, 4, 1, 1.0, 1, None, 0, None) == -2
     assert h.pamk_matmul(0, ptr, ptr, ptr, 1, 4, 4, 64, 0, 64, 1, 0, 4, 1, 1.0, 4, None, 0, None) == -4
     assert h.pamk_matmul_workspace_bytes(2, 3, 5, 4) == 2 * 3 * 5 * 4 * 4
+
+
+def test_nvtx_wrapper_marks_only_entry_points_that_launch():
+    """With tracing on, entry points that take a stream are wrapped in an NVTX range; helpers that only
+    compute sizes or plans are passed through untouched."""
+    from pam_b200 import _lib
+    plain = _lib.lib()
+    _lib.set_nvtx(True)
+    try:
+        traced = _lib.lib()
+        assert traced is not plain
+        assert traced.pamk_matmul_auto_split(1, 64, 64, 64) == plain.pamk_matmul_auto_split(1, 64, 64, 64)
+        assert traced.pamk_softmax_max_len is not None and not hasattr(traced.pamk_softmax_max_len, "__wrapped_name__")
+        assert getattr(traced.pamk_matmul, "__name__", "") == "wrapped"
+        assert getattr(traced.pamk_matmul_workspace_bytes, "__name__", "") != "wrapped"
+    finally:
+        _lib.set_nvtx(False)
+    assert _lib.lib() is plain

@@ -78,3 +78,18 @@ def test_strided_product_rejects_bad_arguments():
     assert call(sa=(768, 256, 2, 3)) == -3                        # no unit stride in the matrix part
     assert call(split=2) == -4                               # an explicit split needs its scratch
     assert call(outer=0) == 0
+
+
+def test_nvtx_ranges_do_not_change_results():
+    import pam_b200 as pam
+    dev = torch.device("cuda", 0)
+    a, b = torch.randn(70, 50, device=dev), torch.randn(50, 30, device=dev)
+    plain = pam.matmul(a, b)
+    pam.set_nvtx(True)
+    try:
+        traced = pam.matmul(a, b)
+        probs = pam.softmax(traced, dim=-1)
+    finally:
+        pam.set_nvtx(False)
+    assert_bits_equal(traced, plain, "matmul under NVTX ranges")
+    assert_bits_equal(probs, pam.softmax(plain, dim=-1), "softmax under NVTX ranges")
