@@ -36,12 +36,20 @@ def test_full_batch_step_against_reference_fixture(name):
     loss.backward()
     want = torch.from_numpy(data[f"{name}/loss"])
     assert_close_nan(loss.detach().reshape(1), want, 2e-5, 0.0, "loss")
-    worst = 0.0
+    worst, failures = 0.0, []
     for k, leaf in leaves.items():
         ref = torch.from_numpy(data[f"{name}/grad/{k}"])
         scale = float(data[f"{name}/grad_max/{k}"][0])
         got = sample(leaf.grad).cpu()
-        if scale > 0:
+        # The gradient of a key projection's bias is zero in exact arithmetic (a constant added to every key
+        # shifts all scores of a row alike, and softmax does not see it): both sides hold the rounding residue
+        # of sums over all tokens, two orders of magnitude below the other biases' gradients.
+        tol = 2e-2 if k.endswith(".k.b") else 2e-3
+        if scale > 0 and not k.endswith(".k.b"):
             worst = max(worst, float((got - ref).abs().max()) / scale)
-        assert_close_nan(got, ref, 2e-3, 2e-3 * scale + 1e-12, f"grad {k}")
+        try:
+            assert_close_nan(got, ref, tol, tol * scale + 1e-12, f"grad {k}")
+        except AssertionError as err:
+            failures.append(str(err))
     print(f"{name}: largest sampled gradient deviation relative to the tensor's maximum: {worst:.2e}")
+    assert not failures, "\n".join(failures)

@@ -209,7 +209,11 @@ def test_exp_log_against_oracle(pam, K, dev, base, offset):
     n = 500_000
     x = torch.cat([torch.randn(n, generator=g) * 30, _wide(n, g, 60), inject(torch.randn(1000, generator=g), 0.5, g,
                   extra=(float("inf"), float("-inf"), float("nan"), 127.5, -126.5, -149.5, 128.0)),
-                   torch.arange(-170, 140).float(), torch.arange(-170, 140).float() - 2.0 ** -18])
+                   torch.arange(-170, 140).float(), torch.arange(-170, 140).float() - 2.0 ** -18,
+                   # results that are denormal, zero or infinite, and exponents far outside fp32's range
+                   torch.arange(-320, 320).float() + 0.37, torch.arange(-160, -120).float() + 0.999999,
+                   torch.tensor([-252.0, -252.5, -253.0, -251.5, 253.5, 254.0, 254.5, 255.0, 1e30, -1e30, 3e38, -3e38,
+                                 -149.0, -150.0, -150.5, -151.0, 127.999, 128.5, -126.0, -127.0])])
     dy = _wide(x.numel(), g, 30)
     ck = pam.cuda_bindings.cuda_kernels
     xd, dd = x.to(dev), dy.to(dev)
