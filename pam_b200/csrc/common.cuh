@@ -26,4 +26,13 @@ inline int check_launch() {
 
 __host__ __device__ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+#if defined(__CUDACC__)
+// Asks the L2 for the `count` floats at p (a row this group of `group` threads will load in its next
+// pass), one request per 128-byte line, so that the DRAM reads of the next row are in flight while the
+// current one is computed; nothing is held in registers.
+__device__ __forceinline__ void prefetch_row_l2(const float* p, int count, int t, int group) {
+    for (int c = t * 32; c < count; c += group * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + c));
+}
+#endif
+
 }  // namespace pamk

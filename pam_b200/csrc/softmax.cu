@@ -156,6 +156,11 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
     for (int64_t row = (int64_t)blockIdx.x * kRowsPerCta + sub; row < a.rows; row += (int64_t)gridDim.x * kRowsPerCta) {
         R x, e;
         x.load(a.x + row * a.len, a.len, t, -INFINITY);       // padding behaves like a masked entry
+        const int64_t next = row + (int64_t)gridDim.x * kRowsPerCta;
+        if (next < a.rows) {
+            prefetch_row_l2(a.x + next * a.len, a.len, t, WARPS * 32);
+            if (OP == kSoftmaxBwd) prefetch_row_l2(a.g + next * a.len, a.len, t, WARPS * 32);
+        }
         float part = 0.0f;
 #pragma unroll
         for (int i = 0; i < NCH * VEC; ++i) {
