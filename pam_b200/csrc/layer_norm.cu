@@ -173,11 +173,6 @@ __global__ void __launch_bounds__(kThreads, VEC * NCH <= 16 ? 6 : 1) ln_fwd_kern
             const int64_t row = row0 + r < a.rows ? row0 + r : a.rows - 1;
             load_row<VEC, NCH, FULL>(c[r], a.x + row * a.width, a.width, lane, 0.0f);
         }
-        if (row0 + nwarps * kRows < a.rows) {                 // this warp's next rows: towards the L2 now
-            const int64_t n0 = row0 + nwarps * kRows;
-            const int64_t count = (n0 + kRows <= a.rows ? kRows : a.rows - n0) * a.width;
-            prefetch_row_l2(a.x + n0 * a.width, (int)count, lane, 32);
-        }
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
             float s = 0.0f;
@@ -259,12 +254,6 @@ __global__ void __launch_bounds__(kThreads, VEC * NCH <= 16 ? 3 : 1) ln_bwd_kern
             const int64_t row = row0 + r < a.rows ? row0 + r : a.rows - 1;     // (beyond the end: computed, not stored)
             load_row<VEC, NCH, FULL>(c[r], a.x + row * a.width, a.width, lane, 0.0f);
             load_row<VEC, NCH, FULL>(g[r], a.dy + row * a.width, a.width, lane, 0.0f);
-        }
-        if (row0 + nwarps * kRows < a.rows) {                 // this warp's next rows: towards the L2 now
-            const int64_t n0 = row0 + nwarps * kRows;
-            const int64_t count = (n0 + kRows <= a.rows ? kRows : a.rows - n0) * a.width;
-            prefetch_row_l2(a.x + n0 * a.width, (int)count, lane, 32);
-            prefetch_row_l2(a.dy + n0 * a.width, (int)count, lane, 32);
         }
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {

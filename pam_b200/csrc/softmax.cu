@@ -156,10 +156,12 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
     for (int64_t row = (int64_t)blockIdx.x * kRowsPerCta + sub; row < a.rows; row += (int64_t)gridDim.x * kRowsPerCta) {
         R x, e;
         x.load(a.x + row * a.len, a.len, t, -INFINITY);       // padding behaves like a masked entry
-        const int64_t next = row + (int64_t)gridDim.x * kRowsPerCta;
-        if (next < a.rows) {
-            prefetch_row_l2(a.x + next * a.len, a.len, t, WARPS * 32);
-            if (OP == kSoftmaxBwd) prefetch_row_l2(a.g + next * a.len, a.len, t, WARPS * 32);
+        // forward kernels: this group's next row towards the L2 while the current one is computed (measured
+        // on 1024-long rows: forward 169 -> 156 us per 2^26 elements; the backward kernels, which hold three
+        // rows in registers at 12 warps per SM, lose a little with it)
+        if (OP == kSoftmaxFwd || OP == kLseFwd || OP == kLossFwd) {
+            const int64_t next = row + (int64_t)gridDim.x * kRowsPerCta;
+            if (next < a.rows) prefetch_row_l2(a.x + next * a.len, a.len, t, WARPS * 32);
         }
         float part = 0.0f;
 #pragma unroll
