@@ -168,7 +168,10 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
         for (int i = 0; i < NCH * VEC; ++i) {
             const bool masked = x.v[i] == -INFINITY;
             const float adj = fadd(scaled_of(x.v[i], off), -shift);
-            const float big = exp_base(adj, lb2, off);
+            // (forward kernels and the exact backward measured faster with the compact form, the
+            // approximate backward kernels with the inlined one)
+            constexpr bool kCompact = OP == kSoftmaxFwd || OP == kLseFwd || OP == kLossFwd || (OP == kSoftmaxBwd && !APPROX);
+            const float big = kCompact ? exp2_compact(mul(adj, lb2, off)) : exp_base(adj, lb2, off);
             e.v[i] = (OP == kSoftmaxFwd || OP == kSoftmaxBwd || OP == kCeBwd) && masked ? 0.0f : big;
             if (R::col(i, t) < a.len) part = fadd(part, e.v[i]);
         }
@@ -309,12 +312,20 @@ int launch_rows(const RowArgs& a, cudaStream_t st) {
         row_kernel<OP, APPROX, V, N, W><<<(unsigned)(want < cap ? want : cap), (W) == 1 ? 128 : (W) * 32, 0, st>>>(a); \
         return check_launch();                                                                          \
     } while (0)
+    // (the number of chunks per thread only sets how many register slots a row may fill: a shorter layout
+    // for a shorter row leaves fewer idle slots and changes no sum, every thread adds its columns in the
+    // same order either way)
     if (vec) {
+        if (a.len <= 128) PAMK_ROWS(4, 1, 1);
         if (a.len <= 256) PAMK_ROWS(4, 2, 1);
+        if (a.len <= 512) PAMK_ROWS(4, 4, 1);
         if (a.len <= 1024) PAMK_ROWS(4, 8, 1);
         if (a.len <= 4096) PAMK_ROWS(4, 4, 8);
         if (a.len <= kMaxLen) PAMK_ROWS(4, 12, 8);
     } else {
+        if (a.len <= 64) PAMK_ROWS(1, 2, 1);
+        if (a.len <= 128) PAMK_ROWS(1, 4, 1);
+        if (a.len <= 224) PAMK_ROWS(1, 7, 1);
         if (a.len <= 256) PAMK_ROWS(1, 8, 1);
         if (a.len <= 1024) PAMK_ROWS(1, 32, 1);
         if (a.len <= kMaxLen) PAMK_ROWS(1, 48, 8);

@@ -623,7 +623,7 @@ def _row_order(length):
     return vec, (1 if length <= 1024 else 8)
 
 
-@pytest.mark.parametrize("length", [1, 5, 32, 197, 200, 1000, 1024, 1028, 4096, 10000])
+@pytest.mark.parametrize("length", [1, 5, 32, 60, 64, 100, 128, 130, 197, 200, 224, 225, 256, 300, 512, 516, 1000, 1024, 1028, 4096, 10000])
 @pytest.mark.parametrize("approx", [True, False])
 def test_fused_softmax_logsumexp_bit_exact_against_replayed_chain(pam, dev, length, approx):
     import ln_emulation as E
