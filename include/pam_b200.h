@@ -220,6 +220,16 @@ int pamk_softmax_fwd(const float* x, float* y, int64_t rows, int64_t len, float 
                      void* workspace, size_t workspace_bytes, void* stream);
 int pamk_softmax_bwd(const float* x, const float* dy, float* dx, int64_t rows, int64_t len, float offset,
                      int approx_bwd, void* workspace, size_t workspace_bytes, void* stream);
+/* The approximate backward pass (approx_bwd) without recomputing the forward chain: pamk_softmax_fwd_save
+ * is pamk_softmax_fwd that also writes the exponentials e = exp2_op(s - shift) ([rows, len]; -0.0f
+ * where x was -inf, so that masked entries stay distinguishable from exponentials that underflowed), and
+ * pamk_softmax_bwd_saved computes from e and dy what pamk_softmax_bwd(..., approx_bwd = 1) computes from
+ * x and dy, bit for bit (optionally followed by the PAM multiplication by post_scale of
+ * pamk_softmax_bwd_scaled): no maximum pass, no workspace, 12 B/element. */
+int pamk_softmax_fwd_save(const float* x, float* y, float* e, int64_t rows, int64_t len, float offset,
+                          void* workspace, size_t workspace_bytes, void* stream);
+int pamk_softmax_bwd_saved(const float* e, const float* dy, float* dx, int64_t rows, int64_t len, float offset,
+                           int has_post_scale, float post_scale, void* stream);
 /* pamk_softmax_bwd followed by a PAM multiplication of dx by post_scale, in the same pass: the
  * gradient of softmax(pam(scores, scale)) with respect to the scores when the scaling's backward
  * is the approximate form pam(d, scale) (pam/cuda_bindings.py:39-50 with approx_bwd). */

@@ -52,6 +52,8 @@ _SIGNATURES = {
     "pamk_softmax_workspace_bytes": (_sz, [_i64, _i64]),
     "pamk_softmax_fwd": (_i, [_p, _p, _i64, _i64, _f, _p, _sz, _p]),
     "pamk_softmax_bwd": (_i, [_p, _p, _p, _i64, _i64, _f, _i, _p, _sz, _p]),
+    "pamk_softmax_fwd_save": (_i, [_p, _p, _p, _i64, _i64, _f, _p, _sz, _p]),
+    "pamk_softmax_bwd_saved": (_i, [_p, _p, _p, _i64, _i64, _f, _i, _f, _p]),
     "pamk_softmax_bwd_scaled": (_i, [_p, _p, _p, _i64, _i64, _f, _i, _f, _p, _sz, _p]),
     "pamk_matmul_strided": (_i, [_p, _p, _p] + [_i64] * 16 + [_f, _i, _f, _i, _p, _sz, _p]),
     "pamk_logsumexp_fwd": (_i, [_p, _p, _i64, _i64, _f, _p, _sz, _p]),

@@ -83,6 +83,8 @@ struct RowArgs {
     long long ignore;        // rows whose target equals this contribute nothing (when has_ignore)
     int has_ignore;
     float c0, c1, c2;        // cross-entropy gradient: hot / cold target probability, row count (0 = no mean)
+    float* aux;              // softmax forward: optional second output, the exponentials e (-0.0f where the
+                             // input was -inf) for kSoftmaxBwdSaved, which takes them as x
     int post;                // softmax backward: multiply dx by post_scale (PAM product) before it is stored,
     float post_scale;        // the gradient of a PAM scaling of the scores by a constant (approx_bwd form)
 };
@@ -140,7 +142,9 @@ __device__ __forceinline__ float group_sum(float s, float* scratch) {
 // kLossFwd / kLossBwd: label-smoothed negative log-likelihood straight from the logits (log-softmax,
 // gather and row sum of fairseq's label_smoothed_nll_loss fused into the logsumexp row pass).
 // kCeBwd: the gradient of pam_opt.cross_entropy (softmax - target distribution, PAM-scaled).
-enum Op { kSoftmaxFwd, kSoftmaxBwd, kLseFwd, kLseBwd, kLossFwd, kLossBwd, kCeBwd };
+// kSoftmaxBwdSaved: the approximate softmax backward from the exponentials the forward pass saved
+// (RowArgs::aux) instead of the input: no maximum pass and no exp2 chain.
+enum Op { kSoftmaxFwd, kSoftmaxBwd, kLseFwd, kLseBwd, kLossFwd, kLossBwd, kCeBwd, kSoftmaxBwdSaved };
 
 template <int OP, bool APPROX, int VEC, int NCH, int WARPS>
 __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(const RowArgs a) {
@@ -148,7 +152,7 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
     constexpr int kRowsPerCta = WARPS == 1 ? 4 : 1;
     const int t = WARPS == 1 ? (threadIdx.x & 31) : threadIdx.x;
     const int sub = WARPS == 1 ? (threadIdx.x >> 5) : 0;
-    const float shift = load_shift(a.partials, a.partial_count);
+    const float shift = OP == kSoftmaxBwdSaved ? 0.0f : load_shift(a.partials, a.partial_count);
     const float lb2 = log2f(2.0f);
     const int32_t off = a.off;
     using R = Row<VEC, NCH, WARPS>;
@@ -164,6 +168,16 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
             if (next < a.rows) prefetch_row_l2(a.x + next * a.len, a.len, t, WARPS * 32);
         }
         float part = 0.0f;
+        if constexpr (OP == kSoftmaxBwdSaved) {
+            // x holds the saved exponentials; padding was loaded as -inf and counts as masked
+#pragma unroll
+            for (int i = 0; i < NCH * VEC; ++i) {
+                const bool masked = f2i(x.v[i]) == (int32_t)0x80000000 || R::col(i, t) >= a.len;
+                e.v[i] = masked ? 0.0f : x.v[i];
+                x.v[i] = masked ? -INFINITY : 0.0f;            // keeps only "masked or not" for the code below
+                if (R::col(i, t) < a.len) part = fadd(part, e.v[i]);
+            }
+        } else
 #pragma unroll
         for (int i = 0; i < NCH * VEC; ++i) {
             const bool masked = x.v[i] == -INFINITY;
@@ -178,6 +192,12 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
         const float total = group_sum<WARPS>(part, scratch);
 
         if (OP == kSoftmaxFwd) {
+            if (a.aux) {                                       // e for the backward pass, masked entries as -0.0f
+                R keep;
+#pragma unroll
+                for (int i = 0; i < NCH * VEC; ++i) keep.v[i] = x.v[i] == -INFINITY ? -0.0f : e.v[i];
+                keep.store(a.aux + row * a.len, a.len, t);
+            }
             const Divisor by_total = make_divisor(total, off);
 #pragma unroll
             for (int i = 0; i < NCH * VEC; ++i) e.v[i] = div_by(e.v[i], by_total);
@@ -254,7 +274,7 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
             // log2 of the row sum runs with offset 0 whatever the call's offset (pam_ops.py:341)
             const float res = div(fadd(shift, log_base(total, lb2, 0)), kLog2e, off);
             if (t == 0) a.out[row] = res;
-        } else if (OP == kSoftmaxBwd) {
+        } else if (OP == kSoftmaxBwd || OP == kSoftmaxBwdSaved) {
             R g;
             g.load(a.g + row * a.len, a.len, t, 0.0f);
             const Divisor by_total = make_divisor(total, off);
@@ -303,7 +323,7 @@ constexpr int kMaxLen = 12288;
 template <int OP, bool APPROX>
 int launch_rows(const RowArgs& a, cudaStream_t st) {
     const bool vec = (a.len & 3) == 0 && aligned16(a.x) && (OP == kLseFwd || OP == kLossFwd || aligned16(a.out)) &&
-                     (OP != kSoftmaxBwd || aligned16(a.g));
+                     ((OP != kSoftmaxBwd && OP != kSoftmaxBwdSaved) || aligned16(a.g)) && (a.aux == nullptr || aligned16(a.aux));
     const int64_t sms = sm_count();
 #define PAMK_ROWS(V, N, W)                                                                              \
     do {                                                                                                \
@@ -345,14 +365,20 @@ int run_rows(int op, bool approx, RowArgs a, int64_t len, float offset, void* wo
     if (rows < 0 || len <= 0) return PAMK_ERR_ARG;
     if (len > kMaxLen) return PAMK_ERR_SIZE;
     if (rows == 0) return PAMK_OK;
-    if (!a.x || !a.out || ((op == kSoftmaxBwd || op == kLseBwd || op == kCeBwd || op == kLossBwd) && !a.g)) return PAMK_ERR_ARG;
+    if (!a.x || !a.out || ((op == kSoftmaxBwd || op == kSoftmaxBwdSaved || op == kLseBwd || op == kCeBwd || op == kLossBwd) && !a.g))
+        return PAMK_ERR_ARG;
     if ((op == kLossFwd || op == kLossBwd || op == kCeBwd) && !a.target) return PAMK_ERR_ARG;
     const int64_t n = rows * len;
     const int grid = max_grid(n);
-    if (!workspace || workspace_bytes < (size_t)grid * sizeof(float) || (reinterpret_cast<uintptr_t>(workspace) & 15u))
-        return PAMK_ERR_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int32_t off = offset_bits(offset);
+    if (op == kSoftmaxBwdSaved) {                     // works from the saved exponentials: no maximum pass
+        a.len = (int)len;
+        a.off = off;
+        return launch_rows<kSoftmaxBwdSaved, true>(a, st);
+    }
+    if (!workspace || workspace_bytes < (size_t)grid * sizeof(float) || (reinterpret_cast<uintptr_t>(workspace) & 15u))
+        return PAMK_ERR_WORKSPACE;
     float* partials = static_cast<float*>(workspace);
     scaled_max_kernel<<<grid, 256, 0, st>>>(a.x, n, off, partials);
     int rc = check_launch();
@@ -400,6 +426,22 @@ int pamk_softmax_fwd(const float* x, float* y, int64_t rows, int64_t len, float 
 int pamk_softmax_bwd(const float* x, const float* dy, float* dx, int64_t rows, int64_t len, float offset,
                      int approx_bwd, void* workspace, size_t workspace_bytes, void* stream) {
     return run_rows(kSoftmaxBwd, approx_bwd != 0, plain_rows(x, dy, dx, rows), len, offset, workspace, workspace_bytes, stream);
+}
+
+int pamk_softmax_fwd_save(const float* x, float* y, float* e, int64_t rows, int64_t len, float offset,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+    if (!e) return PAMK_ERR_ARG;
+    RowArgs a = plain_rows(x, nullptr, y, rows);
+    a.aux = e;
+    return run_rows(kSoftmaxFwd, false, a, len, offset, workspace, workspace_bytes, stream);
+}
+
+int pamk_softmax_bwd_saved(const float* e, const float* dy, float* dx, int64_t rows, int64_t len, float offset,
+                           int has_post_scale, float post_scale, void* stream) {
+    RowArgs a = plain_rows(e, dy, dx, rows);
+    a.post = has_post_scale != 0;
+    a.post_scale = post_scale;
+    return run_rows(kSoftmaxBwdSaved, true, a, len, offset, nullptr, 0, stream);
 }
 
 int pamk_softmax_bwd_scaled(const float* x, const float* dy, float* dx, int64_t rows, int64_t len, float offset,

@@ -124,20 +124,48 @@ def _rows(handle, name, x2, extra, out, offset, approx=None):
     return out
 
 
+def _softmax_forward_saving(x2, offset):
+    """Softmax of the rows of x2 plus the exponentials the approximate backward pass works from."""
+    y, e = torch.empty_like(x2), torch.empty_like(x2)
+    _rows(_lib.lib(), "pamk_softmax_fwd_save", x2, [y], e, offset)
+    return y, e
+
+
+def _softmax_backward_saved(e, g2, offset, post_scale=None):
+    dev = e.device
+    dx = torch.empty_like(e)
+    rows, length = e.shape
+    with _lib.device_guard(dev):
+        status = _lib.lib().pamk_softmax_bwd_saved(e.data_ptr(), g2.data_ptr(), dx.data_ptr(), rows, length, offset,
+                                                   int(post_scale is not None), float(post_scale or 0.0),
+                                                   _lib.stream_ptr(dev))
+    _lib.check(status, "pamk_softmax_bwd_saved")
+    return dx
+
+
 class _Softmax(torch.autograd.Function):
+    """With the approximate backward the forward pass keeps its exponentials instead of its input: the
+    backward pass then needs neither the maximum pass nor the exp2 chain (same values either way)."""
+
     @staticmethod
     def forward(ctx, x, offset, approx):
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
-        ctx.save_for_backward(x2)
         ctx.cfg = (offset, approx, x.shape)
+        if approx and ctx.needs_input_grad[0]:
+            y, e = _softmax_forward_saving(x2, offset)
+            ctx.save_for_backward(e)
+            return y.view(x.shape)
+        ctx.save_for_backward(x2)
         return _rows(_lib.lib(), "pamk_softmax_fwd", x2, [], torch.empty_like(x2), offset).view(x.shape)
 
     @staticmethod
     def backward(ctx, g):
-        (x2,) = ctx.saved_tensors
+        (saved,) = ctx.saved_tensors
         offset, approx, shape = ctx.cfg
-        g2 = g.reshape(x2.shape).contiguous()
-        dx = _rows(_lib.lib(), "pamk_softmax_bwd", x2, [g2], torch.empty_like(x2), offset, approx)
+        g2 = g.reshape(saved.shape).contiguous()
+        if approx:
+            return _softmax_backward_saved(saved, g2, offset).view(shape), None, None
+        dx = _rows(_lib.lib(), "pamk_softmax_bwd", saved, [g2], torch.empty_like(saved), offset, approx)
         return dx.view(shape), None, None
 
 
@@ -222,18 +250,18 @@ class _AttentionQKV(torch.autograd.Function):
         # scores = pam(q k^T, scale): q rows and k rows are 3C apart, heads hd apart
         _strided_product(dev, q_ptr, k_ptr, scores.data_ptr(), B, heads, N, N, hd,
                          (N * C3, hd, C3, 1), (N * C3, hd, 1, C3), (heads * N * N, N * N, N), offset, post_scale=scale)
-        probs = _rows(_lib.lib(), "pamk_softmax_fwd", scores.view(-1, N), [], torch.empty_like(scores).view(-1, N), offset)
+        probs, expo = _softmax_forward_saving(scores.view(-1, N), offset)
         out = torch.empty(B, N, C, dtype=torch.float32, device=dev)
         # context[b, i, h, :] = probs[b, h, i, :] v[b, :, h, :]
         _strided_product(dev, probs.data_ptr(), v_ptr, out.data_ptr(), B, heads, N, hd, N,
                          (heads * N * N, N * N, N, 1), (N * C3, hd, C3, 1), (N * C, hd, C), offset)
-        ctx.save_for_backward(qkv, scores, probs)
+        ctx.save_for_backward(qkv, expo, probs)
         ctx.cfg = (heads, scale, offset)
         return out
 
     @staticmethod
     def backward(ctx, g):
-        qkv, scores, probs = ctx.saved_tensors
+        qkv, expo, probs = ctx.saved_tensors
         heads, scale, offset = ctx.cfg
         B, N, C3 = qkv.shape
         C = C3 // 3
@@ -246,22 +274,14 @@ class _AttentionQKV(torch.autograd.Function):
         dq_ptr, dv_ptr = dqkv.data_ptr(), dqkv.data_ptr() + 8 * C
         s_probs, s_ctx = (heads * N * N, N * N, N, 1), (N * C, hd, C, 1)
         # d probs = d context v^T
-        dprobs = torch.empty_like(scores)
+        dprobs = torch.empty(B * heads, N, N, dtype=torch.float32, device=dev)
         _strided_product(dev, g.data_ptr(), v_ptr, dprobs.data_ptr(), B, heads, N, N, hd,
                          s_ctx, (N * C3, hd, 1, C3), (heads * N * N, N * N, N), offset)
         # d v = probs^T d context, written where v's gradient lives in d qkv
         _strided_product(dev, probs.data_ptr(), g.data_ptr(), dv_ptr, B, heads, N, hd, N,
                          (heads * N * N, N * N, 1, N), (N * C, hd, C, 1), (N * C3, hd, C3), offset)
-        # d scores = pam(softmax backward, scale)
-        dscores = torch.empty_like(scores).view(-1, N)
-        rows = dscores.shape[0]
-        handle = _lib.lib()
-        ws_bytes = handle.pamk_softmax_workspace_bytes(rows, N)
-        ws = _workspace(dev, ws_bytes)
-        with _lib.device_guard(dev):
-            status = handle.pamk_softmax_bwd_scaled(scores.data_ptr(), dprobs.data_ptr(), dscores.data_ptr(), rows, N,
-                                                    offset, 1, scale, ws.data_ptr(), ws_bytes, _lib.stream_ptr(dev))
-        _lib.check(status, "pamk_softmax_bwd_scaled")
+        # d scores = pam(softmax backward, scale), from the exponentials the forward pass kept
+        dscores = _softmax_backward_saved(expo, dprobs.view(-1, N), offset, post_scale=scale)
         # d q = d scores k
         _strided_product(dev, dscores.data_ptr(), k_ptr, dq_ptr, B, heads, N, hd, N,
                          s_probs, (N * C3, hd, C3, 1), (N * C3, hd, C3), offset)

@@ -787,3 +787,41 @@ def test_column_sum(pam, dev, rows, cols):
     # a view with a row stride is gathered first
     wide = torch.randn(rows, cols + 3, generator=g).to(dev)
     assert torch.equal(cb._column_sum(wide[:, :cols]), cb._column_sum(wide[:, :cols].contiguous()))
+
+
+@pytest.mark.parametrize("length", [5, 64, 197, 512, 1024, 4096, 10000])
+@pytest.mark.parametrize("offset", [1.0, 1.0552])
+def test_softmax_backward_from_saved_exponentials(pam, dev, length, offset):
+    """pamk_softmax_fwd_save + pamk_softmax_bwd_saved against pamk_softmax_fwd + pamk_softmax_bwd(approx):
+    the same bits, also where entries are masked (-inf), where exponentials underflow to zero, and where
+    the incoming gradient is inf / NaN on such entries (a masked entry's gradient is 0 whatever arrives,
+    an underflowed one's is NaN when inf arrives)."""
+    from pam_b200 import _lib
+    handle = _lib.lib()
+    g = torch.Generator().manual_seed(length)
+    rows = 37
+    x = torch.randn(rows, length, generator=g) * 4
+    x[::3, : max(1, length // 4)] = float("-inf")                 # masks
+    x[1::5, -1] = -400.0                                          # exponentials that underflow to +0
+    x[5] = float("-inf")                                          # a fully masked row
+    dy = torch.randn(rows, length, generator=g)
+    dy[0, 0] = float("inf")                                       # on a masked entry
+    dy[1, -1] = float("inf")                                      # on an underflowed entry
+    dy[2, length // 2] = float("nan")
+    xd, dyd = x.to(dev), dy.to(dev)
+    st = _lib.stream_ptr(dev)
+    wsb = handle.pamk_softmax_workspace_bytes(rows, length)
+    ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+    y0, y1, e, dx0, dx1, dx2 = (torch.empty_like(xd) for _ in range(6))
+    with _lib.device_guard(dev):
+        assert handle.pamk_softmax_fwd(xd.data_ptr(), y0.data_ptr(), rows, length, offset, ws.data_ptr(), wsb, st) == 0
+        assert handle.pamk_softmax_fwd_save(xd.data_ptr(), y1.data_ptr(), e.data_ptr(), rows, length, offset, ws.data_ptr(), wsb, st) == 0
+        assert handle.pamk_softmax_bwd(xd.data_ptr(), dyd.data_ptr(), dx0.data_ptr(), rows, length, offset, 1, ws.data_ptr(), wsb, st) == 0
+        assert handle.pamk_softmax_bwd_saved(e.data_ptr(), dyd.data_ptr(), dx1.data_ptr(), rows, length, offset, 0, 0.0, st) == 0
+        assert handle.pamk_softmax_bwd_scaled(xd.data_ptr(), dyd.data_ptr(), dx2.data_ptr(), rows, length, offset, 1, 0.125, ws.data_ptr(), wsb, st) == 0
+    assert_bits_equal(y1, y0, "forward with the second output")
+    assert_bits_equal(dx1, dx0, "backward from the saved exponentials")
+    with _lib.device_guard(dev):
+        assert handle.pamk_softmax_bwd_saved(e.data_ptr(), dyd.data_ptr(), dx1.data_ptr(), rows, length, offset, 1, 0.125, st) == 0
+    assert_bits_equal(dx1, dx2, "backward from the saved exponentials, scaled")
+    assert bool((dx0[0, 0] == 0).all()) and bool(dx0[5].eq(0).all()), "masked entries get no gradient"
