@@ -159,7 +159,18 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
 
     for (int64_t row = (int64_t)blockIdx.x * kRowsPerCta + sub; row < a.rows; row += (int64_t)gridDim.x * kRowsPerCta) {
         R x, e;
-        x.load(a.x + row * a.len, a.len, t, -INFINITY);       // padding behaves like a masked entry
+        if constexpr (OP == kSoftmaxBwdSaved) {
+            // the saved exponentials; -0.0f marks a masked entry (and the padding) and acts as +0 in every
+            // step below: flushed products and quotients are +0, and x + (-0) = x
+            e.load(a.x + row * a.len, a.len, t, -0.0f);
+            const int64_t next = row + (int64_t)gridDim.x * kRowsPerCta;
+            if (next < a.rows) {                               // (this kernel waits on its loads: 12 warps per SM)
+                prefetch_row_l2(a.x + next * a.len, a.len, t, WARPS * 32);
+                prefetch_row_l2(a.g + next * a.len, a.len, t, WARPS * 32);
+            }
+        } else {
+            x.load(a.x + row * a.len, a.len, t, -INFINITY);   // padding behaves like a masked entry
+        }
         // forward kernels: this group's next row towards the L2 while the current one is computed (measured
         // on 1024-long rows: forward 169 -> 156 us per 2^26 elements; the backward kernels, which hold three
         // rows in registers at 12 warps per SM, lose a little with it)
@@ -169,14 +180,9 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
         }
         float part = 0.0f;
         if constexpr (OP == kSoftmaxBwdSaved) {
-            // x holds the saved exponentials; padding was loaded as -inf and counts as masked
 #pragma unroll
-            for (int i = 0; i < NCH * VEC; ++i) {
-                const bool masked = f2i(x.v[i]) == (int32_t)0x80000000 || R::col(i, t) >= a.len;
-                e.v[i] = masked ? 0.0f : x.v[i];
-                x.v[i] = masked ? -INFINITY : 0.0f;            // keeps only "masked or not" for the code below
+            for (int i = 0; i < NCH * VEC; ++i)
                 if (R::col(i, t) < a.len) part = fadd(part, e.v[i]);
-            }
         } else
 #pragma unroll
         for (int i = 0; i < NCH * VEC; ++i) {
@@ -290,8 +296,8 @@ __global__ void __launch_bounds__(WARPS == 1 ? 128 : WARPS * 32) row_kernel(cons
             const float d_total = group_sum<WARPS>(dsum, scratch);
 #pragma unroll
             for (int i = 0; i < NCH * VEC; ++i) {
-                const bool masked = x.v[i] == -INFINITY;
-                const float adj = fadd(scaled_of(x.v[i], off), -shift);
+                const bool masked = OP == kSoftmaxBwdSaved ? f2i(e.v[i]) == (int32_t)0x80000000 : x.v[i] == -INFINITY;
+                const float adj = OP == kSoftmaxBwdSaved ? 0.0f : fadd(scaled_of(x.v[i], off), -shift);
                 const float d_big = masked ? 0.0f : fadd(g.v[i], d_total);
                 const float d_adj = APPROX ? mul(mul(e.v[i], kLn2, off), d_big, off)
                                            : exp_base_bwd(adj, d_big, lb2, off);

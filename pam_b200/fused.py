@@ -148,10 +148,10 @@ class _Softmax(torch.autograd.Function):
     backward pass then needs neither the maximum pass nor the exp2 chain (same values either way)."""
 
     @staticmethod
-    def forward(ctx, x, offset, approx):
+    def forward(ctx, x, offset, approx, keep):
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
         ctx.cfg = (offset, approx, x.shape)
-        if approx and ctx.needs_input_grad[0]:
+        if approx and keep:
             y, e = _softmax_forward_saving(x2, offset)
             ctx.save_for_backward(e)
             return y.view(x.shape)
@@ -164,9 +164,9 @@ class _Softmax(torch.autograd.Function):
         offset, approx, shape = ctx.cfg
         g2 = g.reshape(saved.shape).contiguous()
         if approx:
-            return _softmax_backward_saved(saved, g2, offset).view(shape), None, None
+            return _softmax_backward_saved(saved, g2, offset).view(shape), None, None, None
         dx = _rows(_lib.lib(), "pamk_softmax_bwd", saved, [g2], torch.empty_like(saved), offset, approx)
-        return dx.view(shape), None, None
+        return dx.view(shape), None, None, None
 
 
 class _LogSumExp(torch.autograd.Function):
@@ -192,7 +192,8 @@ def _flag(approx_bwd):
 
 
 def softmax(x, dim, *, offset=None, approx_bwd=False):
-    return _Softmax.apply(x, _offset(offset), _flag(approx_bwd))
+    # (the exponentials are only worth writing when a backward pass can follow)
+    return _Softmax.apply(x, _offset(offset), _flag(approx_bwd), torch.is_grad_enabled() and x.requires_grad)
 
 
 def logsumexp(x, dim, keepdim=False, *, offset=None, approx_bwd=False):
