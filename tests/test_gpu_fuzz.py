@@ -79,3 +79,47 @@ def test_random_product_against_oracle(oracle, case):
     assert bool(got[ok].isfinite().all()) and bool(want[ok].isfinite().all()), what + ": finite lanes"
     bound = 4 * Kdim * 2.0 ** -24 * terms.double() + 1e-30
     assert bool(((got.double() - want.double()).abs()[ok] <= bound[ok]).all()), what
+
+
+@pytest.mark.parametrize("Kdim", [8, 16, 20, 24, 32, 100])
+@pytest.mark.parametrize("policy", [0, 1, 2])
+@pytest.mark.parametrize("delta_l", [True, False])
+def test_exact_gradient_below_offset_one_against_oracle(oracle, Kdim, policy, delta_l):
+    """Offsets below one make the slope of a zero-padded K-tail term -inf for outputs whose D has a small
+    mantissa: the reference's kernel pads K to a multiple of 32 (pam/cuda_kernels.cu:795-809) and so turns
+    those outputs into NaN exactly when K is not a multiple of 32 - on every tile shape alike."""
+    from pam_b200 import _lib, cuda_bindings as cb
+    K = oracle.kernels()
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(Kdim * 10 + policy)
+    M, N = 70, 45
+    A = torch.randn(M, Kdim, generator=g)
+    B = torch.randn(Kdim, N, generator=g)
+    D = torch.randn(M, N, generator=g)
+    D.view(-1)[::5] = 1.0 + 2.0 ** -20                      # small mantissas
+    _lib.check(_lib.lib().pamk_test_set_tile_policy(policy), "tile policy")
+    try:
+        for offset in (0.97, 0.9):
+            got = cb._matmul_bwd(A.to(dev), B.to(dev), D.to(dev), delta_l, offset, 2, split_k=1)
+            want = K.pam_matmul_bwd(A, B, D, True, True, delta_l, offset)
+            assert_bits_equal(got, want, f"exact gradient, K={Kdim}, offset={offset}")
+            assert bool(want.isnan().any()) == (Kdim % 32 != 0), "NaN appears exactly when K is padded"
+    finally:
+        _lib.lib().pamk_test_set_tile_policy(0)
+
+
+def test_tall_product_beyond_the_grid_limit(oracle):
+    """More than 65535 row tiles of the small tile shapes: the product moves to the 128 x 128 tile instead of
+    being refused.  Rows are sampled against the oracle."""
+    from pam_b200 import cuda_bindings as cb
+    K = oracle.kernels()
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(5)
+    M, N, Kdim = 65536 * 64 + 100, 10, 12                   # 4.19 M rows: beyond 65535 tiles of 64 (and of 32)
+    A = torch.randn(M, Kdim, generator=g, device=dev)
+    B = torch.randn(Kdim, N, generator=g, device=dev)
+    got = cb._matmul(0, A, B, 1.0, 2, split_k=1)
+    rows = torch.cat([torch.arange(0, 300, device=dev), torch.arange(M - 300, M, device=dev),
+                      torch.randint(0, M, (400,), generator=g, device=dev)])
+    want = K.pam_matmul_fwd(A[rows].cpu(), B.cpu(), True, True, 1.0)
+    assert_bits_equal(got[rows], want, "sampled rows of the tall product")
