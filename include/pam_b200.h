@@ -204,6 +204,20 @@ int pamk_layer_norm_bwd(const float* x, const float* weight, const float* dy, fl
                         float* dweight, float* dbias, int64_t rows, int64_t width, float eps, float offset,
                         int approx_bwd, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The approximate backward pass (approx_bwd) without recomputing the forward chain:
+ * pamk_layer_norm_fwd_save is pamk_layer_norm_fwd that also writes, per row, the
+ * pamk_layer_norm_stats_per_row() scalars of the forward chain (mean, variance + eps, its square root
+ * and the exact thresholds of the division by it) into stats ([rows, 8] floats, 16-byte aligned), and
+ * pamk_layer_norm_bwd_saved computes from x, dy and stats what pamk_layer_norm_bwd(..., approx_bwd = 1)
+ * computes from x and dy: dx bit for bit; dweight / dbias the same per-row terms, summed over the rows in
+ * another order (a warp walks two rows per pass instead of four). */
+int pamk_layer_norm_stats_per_row(void);
+int pamk_layer_norm_fwd_save(const float* x, const float* weight, const float* bias, float* y, float* stats,
+                             int64_t rows, int64_t width, float eps, float offset, void* stream);
+int pamk_layer_norm_bwd_saved(const float* x, const float* weight, const float* dy, const float* stats, float* dx,
+                              float* dweight, float* dbias, int64_t rows, int64_t width, float offset,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- fused softmax / logsumexp over the last dimension ----------------------------------------------
  * Replace the launch chains of pam_ops.softmax (pam/pam_ops.py:305-328) and pam_ops.logsumexp
  * (:331-342) and of their autograd:

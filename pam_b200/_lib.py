@@ -46,6 +46,9 @@ _SIGNATURES = {
     "pamk_matmul_bwd_auto_split": (_i, [_i64] * 4),
     "pamk_layer_norm_max_width": (_i, []),
     "pamk_layer_norm_fwd": (_i, [_p, _p, _p, _p, _i64, _i64, _f, _f, _p]),
+    "pamk_layer_norm_stats_per_row": (_i, []),
+    "pamk_layer_norm_fwd_save": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _f, _f, _p]),
+    "pamk_layer_norm_bwd_saved": (_i, [_p] * 7 + [_i64, _i64, _f, _p, _sz, _p]),
     "pamk_layer_norm_bwd_workspace_bytes": (_sz, [_i64, _i64]),
     "pamk_layer_norm_bwd": (_i, [_p] * 6 + [_i64, _i64, _f, _f, _i, _p, _sz, _p]),
     "pamk_softmax_max_len": (_i, []),

@@ -56,7 +56,12 @@ struct LnArgs {
     int width;
     float nf, eps;
     int32_t off;
+    float* stats;        // [rows][8] row scalars of the forward chain: written by the forward pass when not
+                         // null, read by the backward pass that works from them (kStat* below)
 };
+
+// What the forward pass keeps per row for the backward pass that does not recompute it.
+enum { kStatMu = 0, kStatV, kStatE, kStatFlushMax, kStatPassMax, kStatSub, kStatRecip, kStatDenom, kStatCount };
 
 // Row-level scalars of the forward chain.
 struct RowStats {
@@ -180,6 +185,7 @@ __global__ void __launch_bounds__(kThreads, VEC * NCH <= 16 ? 6 : 1) ln_fwd_kern
             for (int i = 0; i < NCH * VEC; ++i) s = fadd(s, c[r].v[i]);
             s1[r] = warp_sum(s);
             const float mu = div_by(s1[r], sh.by_n);
+            s1[r] = mu;                                    // (the sum itself is not needed again here)
             s = 0.0f;
 #pragma unroll
             for (int i = 0; i < NCH * VEC; ++i) {
@@ -191,10 +197,19 @@ __global__ void __launch_bounds__(kThreads, VEC * NCH <= 16 ? 6 : 1) ln_fwd_kern
         // the scalar chain of row (lane % kRows), then every row's divisor to every lane
         RowStats mine;
         mine.s2 = s2[0];
+        mine.mu = s1[0];
 #pragma unroll
-        for (int r = 1; r < kRows; ++r) mine.s2 = (lane % kRows) == r ? s2[r] : mine.s2;
+        for (int r = 1; r < kRows; ++r) {
+            mine.s2 = (lane % kRows) == r ? s2[r] : mine.s2;
+            mine.mu = (lane % kRows) == r ? s1[r] : mine.mu;
+        }
         finish_stats(mine, a, sh);
         const Divisor my_divisor = make_divisor(mine.denom, a.off);
+        if (a.stats && lane < kRows && row0 + lane < a.rows) {      // lane r holds the chain of row r
+            float4* out = reinterpret_cast<float4*>(a.stats + (row0 + lane) * kStatCount);
+            out[0] = make_float4(mine.mu, mine.v, mine.e, my_divisor.flush_max);
+            out[1] = make_float4(my_divisor.pass_max, i2f(my_divisor.sub), div_by(1.0f, my_divisor), mine.denom);
+        }
         // weight and bias are re-read per row group (they stay in L1) rather than held in registers
         // for the whole kernel: the registers buy more resident warps
         RowRegs<VEC, NCH> p;
@@ -228,9 +243,16 @@ __global__ void __launch_bounds__(kThreads, VEC * NCH <= 16 ? 6 : 1) ln_fwd_kern
 // and 20 warps measured 5 % slower)
 __host__ __device__ constexpr int rows_per_warp_bwd(int slots) { return slots <= 8 ? 4 : (slots <= 16 ? 2 : 1); }
 
-template <int VEC, int NCH, bool APPROX, bool FULL>
-__global__ void __launch_bounds__(kThreads, VEC * NCH <= 16 ? 3 : 1) ln_bwd_kernel(const LnArgs a) {
-    constexpr int kRows = rows_per_warp_bwd(VEC * NCH);
+// SAVED: the row scalars come from the forward pass (LnArgs::stats) instead of being recomputed from x:
+// no first two row sums and no forward scalar chain, so a warp no longer needs several rows in flight to
+// share that chain, needs fewer registers and more warps fit on an SM (approximate gradients only).
+#ifndef PAMK_LN_SAVED_ROWS
+#define PAMK_LN_SAVED_ROWS 2
+#endif
+template <int VEC, int NCH, bool APPROX, bool FULL, bool SAVED = false>
+__global__ void __launch_bounds__(kThreads, VEC * NCH <= 16 ? (SAVED ? 5 : 3) : 1) ln_bwd_kernel(const LnArgs a) {
+    constexpr int kRows = SAVED ? (VEC * NCH <= 8 ? PAMK_LN_SAVED_ROWS : 1) : rows_per_warp_bwd(VEC * NCH);
+    static_assert(!SAVED || APPROX, "the exact gradients need the forward intermediates recomputed");
     __shared__ float stage[kWarpsPerCta][NCH * VEC][32];
     const int lane = threadIdx.x & 31;
     const int wid = threadIdx.x >> 5;
@@ -255,33 +277,56 @@ __global__ void __launch_bounds__(kThreads, VEC * NCH <= 16 ? 3 : 1) ln_bwd_kern
             load_row<VEC, NCH, FULL>(c[r], a.x + row * a.width, a.width, lane, 0.0f);
             load_row<VEC, NCH, FULL>(g[r], a.dy + row * a.width, a.width, lane, 0.0f);
         }
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-            float s = 0.0f;
-#pragma unroll
-            for (int i = 0; i < NCH * VEC; ++i) s = fadd(s, c[r].v[i]);
-            s1[r] = warp_sum(s);
-            const float mu = div_by(s1[r], sh.by_n);
-            s = 0.0f;
-#pragma unroll
-            for (int i = 0; i < NCH * VEC; ++i) {
-                c[r].v[i] = live<VEC, NCH, FULL>(i, a.width, lane) ? fadd(c[r].v[i], -mu) : 0.0f;
-                s = fadd(s, mul(c[r].v[i], c[r].v[i], a.off));
-            }
-            s2[r] = warp_sum(s);
-        }
         const int my_row = lane % kRows;
         RowStats st;
-        st.s2 = s2[0];
-        st.s1 = s1[0];
+        Divisor my_divisor;
+        float my_recip;
+        if constexpr (SAVED) {
+            // lane L reads the scalars of row L % kRows; the centred rows need every row's mean
+            const int64_t mine = row0 + my_row < a.rows ? row0 + my_row : a.rows - 1;
+            const float4* in = reinterpret_cast<const float4*>(a.stats + mine * kStatCount);
+            const float4 s0 = __ldg(in), s1v = __ldg(in + 1);
+            st.v = s0.y;
+            st.e = s0.z;
+            my_divisor.flush_max = s0.w;
+            my_divisor.pass_max = s1v.x;
+            my_divisor.sub = f2i(s1v.y);
+            my_recip = s1v.z;
+            st.denom = s1v.w;
 #pragma unroll
-        for (int r = 1; r < kRows; ++r) {
-            st.s2 = my_row == r ? s2[r] : st.s2;
-            st.s1 = my_row == r ? s1[r] : st.s1;
+            for (int r = 0; r < kRows; ++r) {
+                const float mu = __shfl_sync(0xffffffffu, s0.x, r);
+#pragma unroll
+                for (int i = 0; i < NCH * VEC; ++i)
+                    c[r].v[i] = live<VEC, NCH, FULL>(i, a.width, lane) ? fadd(c[r].v[i], -mu) : 0.0f;
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                float s = 0.0f;
+#pragma unroll
+                for (int i = 0; i < NCH * VEC; ++i) s = fadd(s, c[r].v[i]);
+                s1[r] = warp_sum(s);
+                const float mu = div_by(s1[r], sh.by_n);
+                s = 0.0f;
+#pragma unroll
+                for (int i = 0; i < NCH * VEC; ++i) {
+                    c[r].v[i] = live<VEC, NCH, FULL>(i, a.width, lane) ? fadd(c[r].v[i], -mu) : 0.0f;
+                    s = fadd(s, mul(c[r].v[i], c[r].v[i], a.off));
+                }
+                s2[r] = warp_sum(s);
+            }
+            st.s2 = s2[0];
+            st.s1 = s1[0];
+#pragma unroll
+            for (int r = 1; r < kRows; ++r) {
+                st.s2 = my_row == r ? s2[r] : st.s2;
+                st.s1 = my_row == r ? s1[r] : st.s1;
+            }
+            finish_stats(st, a, sh);
+            my_divisor = make_divisor(st.denom, a.off);
+            my_recip = div_by(1.0f, my_divisor);
         }
-        finish_stats(st, a, sh);
-        const Divisor my_divisor = make_divisor(st.denom, a.off);
-        const float my_recip = div_by(1.0f, my_divisor);
 
         // d(out)/d(xn), the division's two gradients; g is overwritten by d_c1
         float d_denom[kRows], recip[kRows];
@@ -411,7 +456,7 @@ int pick_grid(int64_t rows, bool backward) {
     return (int)(want < cap ? want : cap);
 }
 
-template <bool BWD, bool APPROX>
+template <bool BWD, bool APPROX, bool SAVED = false>
 int launch(const LnArgs& a, int grid, cudaStream_t st) {
     // register layout: VEC consecutive columns per chunk, NCH chunks per lane; the first layout
     // that holds the row with the fewest register slots wins (192 columns: 3 chunks of 2)
@@ -423,10 +468,10 @@ int launch(const LnArgs& a, int grid, cudaStream_t st) {
 #define PAMK_LN(V, N)                                                                   \
     do {                                                                                \
         if (a.width == 32 * (V) * (N)) {                                                \
-            if (BWD) ln_bwd_kernel<V, N, APPROX, true><<<grid, kThreads, 0, st>>>(a);   \
+            if (BWD) ln_bwd_kernel<V, N, APPROX, true, SAVED><<<grid, kThreads, 0, st>>>(a); \
             else ln_fwd_kernel<V, N, true><<<grid, kThreads, 0, st>>>(a);               \
         } else {                                                                        \
-            if (BWD) ln_bwd_kernel<V, N, APPROX, false><<<grid, kThreads, 0, st>>>(a);  \
+            if (BWD) ln_bwd_kernel<V, N, APPROX, false, SAVED><<<grid, kThreads, 0, st>>>(a); \
             else ln_fwd_kernel<V, N, false><<<grid, kThreads, 0, st>>>(a);              \
         }                                                                               \
         return check_launch();                                                          \
@@ -460,6 +505,45 @@ int pamk_layer_norm_fwd(const float* x, const float* weight, const float* bias, 
     if (!x || !y) return PAMK_ERR_ARG;
     LnArgs a{x, weight, bias, nullptr, y, nullptr, rows, (int)width, (float)width, eps, offset_bits(offset)};
     return launch<false, false>(a, pick_grid(rows, false), static_cast<cudaStream_t>(stream));
+}
+
+int pamk_layer_norm_stats_per_row(void) { return kStatCount; }
+
+int pamk_layer_norm_fwd_save(const float* x, const float* weight, const float* bias, float* y, float* stats,
+                             int64_t rows, int64_t width, float eps, float offset, void* stream) {
+    if (rows < 0 || width <= 0) return PAMK_ERR_ARG;
+    if (width > 1024) return PAMK_ERR_SIZE;
+    if (rows == 0) return PAMK_OK;
+    if (!x || !y || !stats || (reinterpret_cast<uintptr_t>(stats) & 15u)) return PAMK_ERR_ARG;
+    LnArgs a{x, weight, bias, nullptr, y, nullptr, rows, (int)width, (float)width, eps, offset_bits(offset), stats};
+    return launch<false, false>(a, pick_grid(rows, false), static_cast<cudaStream_t>(stream));
+}
+
+int pamk_layer_norm_bwd_saved(const float* x, const float* weight, const float* dy, const float* stats, float* dx,
+                              float* dweight, float* dbias, int64_t rows, int64_t width, float offset,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+    if (rows < 0 || width <= 0) return PAMK_ERR_ARG;
+    if (width > 1024) return PAMK_ERR_SIZE;
+    if (dweight && !weight) return PAMK_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (rows == 0) {
+        if (dweight) cudaMemsetAsync(dweight, 0, width * sizeof(float), st);
+        if (dbias) cudaMemsetAsync(dbias, 0, width * sizeof(float), st);
+        return PAMK_OK;
+    }
+    if (!x || !dy || !dx || !stats || (reinterpret_cast<uintptr_t>(stats) & 15u)) return PAMK_ERR_ARG;
+    const int grid = pick_grid(rows, true);
+    const bool params = dweight || dbias;
+    if (params && (!workspace || workspace_bytes < pamk_layer_norm_bwd_workspace_bytes(rows, width) ||
+                   (reinterpret_cast<uintptr_t>(workspace) & 15u)))
+        return PAMK_ERR_WORKSPACE;
+    LnArgs a{x, weight, nullptr, dy, dx, params ? static_cast<float*>(workspace) : nullptr,
+             rows, (int)width, (float)width, 0.0f, offset_bits(offset), const_cast<float*>(stats)};
+    const int rc = launch<true, true, true>(a, grid, st);
+    if (rc != PAMK_OK || !params) return rc;
+    ln_param_grad_kernel<<<(unsigned)((width + 31) / 32), kGradWarps * 32, 0, st>>>(
+        static_cast<const float*>(workspace), dweight, dbias, grid, (int)width);
+    return check_launch();
 }
 
 size_t pamk_layer_norm_bwd_workspace_bytes(int64_t rows, int64_t width) {

@@ -51,25 +51,35 @@ def layer_norm_supported(x, normalized_shape, weight, bias, approx_bwd=False):
 
 
 class _LayerNorm(torch.autograd.Function):
+    """With the approximate backward (and a backward pass to come) the forward pass also keeps eight
+    scalars per row, and the backward pass works from them instead of recomputing the row statistics."""
+
     @staticmethod
-    def forward(ctx, x, weight, bias, width, eps, offset, approx):
+    def forward(ctx, x, weight, bias, width, eps, offset, approx, keep):
         rows2d = x.reshape(-1, width).contiguous()
         w = weight.contiguous().view(-1) if weight is not None else None
         b = bias.contiguous().view(-1) if bias is not None else None
         y = torch.empty_like(rows2d)
         dev = x.device
+        handle = _lib.lib()
+        stats = None
         with _lib.device_guard(dev):
-            status = _lib.lib().pamk_layer_norm_fwd(rows2d.data_ptr(), _ptr(w), _ptr(b), y.data_ptr(),
+            if approx and keep:
+                stats = torch.empty(rows2d.shape[0], handle.pamk_layer_norm_stats_per_row(), dtype=torch.float32, device=dev)
+                status = handle.pamk_layer_norm_fwd_save(rows2d.data_ptr(), _ptr(w), _ptr(b), y.data_ptr(), stats.data_ptr(),
+                                                         rows2d.shape[0], width, eps, offset, _lib.stream_ptr(dev))
+            else:
+                status = handle.pamk_layer_norm_fwd(rows2d.data_ptr(), _ptr(w), _ptr(b), y.data_ptr(),
                                                     rows2d.shape[0], width, eps, offset, _lib.stream_ptr(dev))
         _lib.check(status, "pamk_layer_norm_fwd")
-        ctx.save_for_backward(rows2d, w)
+        ctx.save_for_backward(rows2d, w, stats)
         ctx.cfg = (width, eps, offset, approx, bias is not None, x.shape,
                    weight.shape if weight is not None else None, bias.shape if bias is not None else None)
         return y.view(x.shape)
 
     @staticmethod
     def backward(ctx, g):
-        rows2d, w = ctx.saved_tensors
+        rows2d, w, stats = ctx.saved_tensors
         width, eps, offset, approx, has_bias, x_shape, w_shape, b_shape = ctx.cfg
         dev = rows2d.device
         g2 = g.reshape(-1, width).contiguous()
@@ -82,18 +92,24 @@ class _LayerNorm(torch.autograd.Function):
         ws_bytes = handle.pamk_layer_norm_bwd_workspace_bytes(rows2d.shape[0], width) if (need_w or need_b) else 0
         ws = _workspace(dev, ws_bytes) if ws_bytes else None
         with _lib.device_guard(dev):
-            status = handle.pamk_layer_norm_bwd(rows2d.data_ptr(), _ptr(w), g2.data_ptr(), dx.data_ptr(), _ptr(dw),
-                                                _ptr(db), rows2d.shape[0], width, eps, offset, int(bool(approx)),
-                                                _ptr(ws), ws_bytes, _lib.stream_ptr(dev))
+            if stats is not None:
+                status = handle.pamk_layer_norm_bwd_saved(rows2d.data_ptr(), _ptr(w), g2.data_ptr(), stats.data_ptr(),
+                                                          dx.data_ptr(), _ptr(dw), _ptr(db), rows2d.shape[0], width,
+                                                          offset, _ptr(ws), ws_bytes, _lib.stream_ptr(dev))
+            else:
+                status = handle.pamk_layer_norm_bwd(rows2d.data_ptr(), _ptr(w), g2.data_ptr(), dx.data_ptr(), _ptr(dw),
+                                                    _ptr(db), rows2d.shape[0], width, eps, offset, int(bool(approx)),
+                                                    _ptr(ws), ws_bytes, _lib.stream_ptr(dev))
         _lib.check(status, "pamk_layer_norm_bwd")
         return (dx.view(x_shape), dw.view(w_shape) if need_w else None, db.view(b_shape) if need_b else None,
-                None, None, None, None)
+                None, None, None, None, None)
 
 
 def layer_norm(x, normalized_shape, weight, bias, eps, *, offset=None, approx_bwd=False):
     if not isinstance(approx_bwd, bool):
         approx_bwd = bool(approx_bwd[0])
-    return _LayerNorm.apply(x, weight, bias, math.prod(normalized_shape), float(eps), _offset(offset), approx_bwd)
+    keep = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (x, weight, bias))
+    return _LayerNorm.apply(x, weight, bias, math.prod(normalized_shape), float(eps), _offset(offset), approx_bwd, keep)
 
 
 # ---- softmax ---------------------------------------------------------------------------------------

@@ -518,9 +518,11 @@ def _ln_vec(width):
     return 4 if width % 4 == 0 else 1
 
 
-def _ln_rows_per_warp(width):
+def _ln_rows_per_warp(width, approx=False):
     """Rows a warp of the backward kernel handles per pass: four for layouts of up to 8 register
-    slots per lane, two up to 16, else one (pam_b200/csrc/layer_norm.cu rows_per_warp_bwd)."""
+    slots per lane, two up to 16, else one (pam_b200/csrc/layer_norm.cu rows_per_warp_bwd); the
+    approximate backward, which works from the row scalars the forward pass saved, takes two rows
+    for layouts of up to 8 slots and one otherwise."""
     vec = _ln_vec(width)
     if vec == 4:
         slots = next(s for cap, s in ((128, 4), (256, 8), (512, 16), (768, 24), (1024, 32)) if width <= cap)
@@ -528,6 +530,8 @@ def _ln_rows_per_warp(width):
         slots = 6
     else:
         slots = 8 if width <= 256 else 32
+    if approx:
+        return 2 if slots <= 8 else 1
     return 4 if slots <= 8 else (2 if slots <= 16 else 1)
 
 
@@ -546,7 +550,7 @@ def _ln_case(pam, dev, rows, width, affine, approx, offset, seed):
     vec = _ln_vec(width)
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     grid = min((rows + 3) // 4, sms * 12)                    # CTAs of the backward kernel
-    chain = E.Chain(offset, E.kernel_rowsum(vec), E.kernel_colsum(rows, grid, rows_per_warp=_ln_rows_per_warp(width)))
+    chain = E.Chain(offset, E.kernel_rowsum(vec), E.kernel_colsum(rows, grid, rows_per_warp=_ln_rows_per_warp(width, approx)))
     want = chain.run(x, w, b, gy, 1e-5, approx)
     got = (y, xd.grad, wd.grad if affine else None, bd.grad if affine else None)
     return got, want
@@ -825,3 +829,42 @@ def test_softmax_backward_from_saved_exponentials(pam, dev, length, offset):
         assert handle.pamk_softmax_bwd_saved(e.data_ptr(), dyd.data_ptr(), dx1.data_ptr(), rows, length, offset, 1, 0.125, st) == 0
     assert_bits_equal(dx1, dx2, "backward from the saved exponentials, scaled")
     assert bool((dx0[0, 0] == 0).all()) and bool(dx0[5].eq(0).all()), "masked entries get no gradient"
+
+
+@pytest.mark.parametrize("width", [5, 48, 192, 200, 512, 1024])
+@pytest.mark.parametrize("affine", [True, False])
+def test_layer_norm_backward_from_saved_row_scalars(pam, dev, width, affine):
+    """pamk_layer_norm_fwd_save + pamk_layer_norm_bwd_saved against pamk_layer_norm_fwd +
+    pamk_layer_norm_bwd(approx): y and dx bit for bit (also for constant rows, whose variance is 0 without
+    eps); dweight / dbias are the same per-row terms summed in another order."""
+    from pam_b200 import _lib
+    handle = _lib.lib()
+    g = torch.Generator().manual_seed(width)
+    rows = 1001
+    x = torch.randn(rows, width, generator=g) * 2 + 0.3
+    x[7] = 1.5                                                     # constant row
+    dy = torch.randn(rows, width, generator=g)
+    w = (torch.randn(width, generator=g).abs() + 0.5).to(dev) if affine else None
+    b = torch.randn(width, generator=g).to(dev) if affine else None
+    xd, dyd = x.to(dev), dy.to(dev)
+    st = _lib.stream_ptr(dev)
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    wsb = handle.pamk_layer_norm_bwd_workspace_bytes(rows, width)
+    ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+    for eps in (1e-5, 0.0):
+        y0, y1, dx0, dx1 = (torch.empty_like(xd) for _ in range(4))
+        stats = torch.empty(rows, handle.pamk_layer_norm_stats_per_row(), device=dev)
+        dw0, db0, dw1, db1 = (torch.empty(width, device=dev) for _ in range(4))
+        with _lib.device_guard(dev):
+            assert handle.pamk_layer_norm_fwd(xd.data_ptr(), ptr(w), ptr(b), y0.data_ptr(), rows, width, eps, 1.0, st) == 0
+            assert handle.pamk_layer_norm_fwd_save(xd.data_ptr(), ptr(w), ptr(b), y1.data_ptr(), stats.data_ptr(), rows, width, eps, 1.0, st) == 0
+            assert handle.pamk_layer_norm_bwd(xd.data_ptr(), ptr(w), dyd.data_ptr(), dx0.data_ptr(), ptr(dw0) if affine else None,
+                                              db0.data_ptr(), rows, width, eps, 1.0, 1, ws.data_ptr(), wsb, st) == 0
+            assert handle.pamk_layer_norm_bwd_saved(xd.data_ptr(), ptr(w), dyd.data_ptr(), stats.data_ptr(), dx1.data_ptr(),
+                                                    ptr(dw1) if affine else None, db1.data_ptr(), rows, width, 1.0,
+                                                    ws.data_ptr(), wsb, st) == 0
+        assert_bits_equal(y1, y0, f"forward with the row scalars, eps={eps}")
+        assert_bits_equal(dx1, dx0, f"dx from the saved row scalars, eps={eps}")
+        assert_close_nan(db1, db0, 1e-5, 1e-5 * float(db0.nan_to_num().abs().max()), "dbias")
+        if affine:      # (without eps the constant row's NaN reaches every column of dweight, on both sides)
+            assert_close_nan(dw1, dw0, 1e-5, 1e-5 * float(dw0.nan_to_num().abs().max()), "dweight")
