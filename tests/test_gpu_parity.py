@@ -627,7 +627,7 @@ def _row_order(length):
     return vec, (1 if length <= 1024 else 8)
 
 
-@pytest.mark.parametrize("length", [1, 5, 32, 60, 64, 100, 128, 130, 197, 200, 224, 225, 256, 300, 512, 516, 1000, 1024, 1028, 4096, 10000])
+@pytest.mark.parametrize("length", [1, 5, 32, 60, 64, 100, 128, 130, 197, 200, 224, 225, 256, 300, 512, 516, 768, 772, 1000, 1024, 1028, 4096, 10000])
 @pytest.mark.parametrize("approx", [True, False])
 def test_fused_softmax_logsumexp_bit_exact_against_replayed_chain(pam, dev, length, approx):
     import ln_emulation as E
@@ -793,7 +793,7 @@ def test_column_sum(pam, dev, rows, cols):
     assert torch.equal(cb._column_sum(wide[:, :cols]), cb._column_sum(wide[:, :cols].contiguous()))
 
 
-@pytest.mark.parametrize("length", [5, 64, 197, 512, 1024, 4096, 10000])
+@pytest.mark.parametrize("length", [5, 64, 197, 512, 768, 1024, 4096, 10000])
 @pytest.mark.parametrize("offset", [1.0, 1.0552])
 def test_softmax_backward_from_saved_exponentials(pam, dev, length, offset):
     """pamk_softmax_fwd_save + pamk_softmax_bwd_saved against pamk_softmax_fwd + pamk_softmax_bwd(approx):
