@@ -162,7 +162,7 @@ constexpr int min_ctas(int slots, bool backward) {
 // still summed and evaluated exactly as if it were alone.
 __host__ __device__ constexpr int rows_per_warp(int slots) { return slots <= 8 ? 4 : (slots <= 16 ? 2 : 1); }
 
-template <int VEC, int NCH, bool FULL>
+template <int VEC, int NCH, bool FULL, bool SAVE = false>
 __global__ void __launch_bounds__(kThreads, VEC * NCH <= 16 ? 6 : 1) ln_fwd_kernel(const LnArgs a) {
     constexpr int kRows = rows_per_warp(VEC * NCH);
     const int lane = threadIdx.x & 31;
@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(kThreads, VEC * NCH <= 16 ? 6 : 1) ln_fwd_kern
             for (int i = 0; i < NCH * VEC; ++i) s = fadd(s, c[r].v[i]);
             s1[r] = warp_sum(s);
             const float mu = div_by(s1[r], sh.by_n);
-            s1[r] = mu;                                    // (the sum itself is not needed again here)
+            if (SAVE) s1[r] = mu;                          // (the sum itself is not needed again here)
             s = 0.0f;
 #pragma unroll
             for (int i = 0; i < NCH * VEC; ++i) {
@@ -197,15 +197,15 @@ __global__ void __launch_bounds__(kThreads, VEC * NCH <= 16 ? 6 : 1) ln_fwd_kern
         // the scalar chain of row (lane % kRows), then every row's divisor to every lane
         RowStats mine;
         mine.s2 = s2[0];
-        mine.mu = s1[0];
+        if (SAVE) mine.mu = s1[0];
 #pragma unroll
         for (int r = 1; r < kRows; ++r) {
             mine.s2 = (lane % kRows) == r ? s2[r] : mine.s2;
-            mine.mu = (lane % kRows) == r ? s1[r] : mine.mu;
+            if (SAVE) mine.mu = (lane % kRows) == r ? s1[r] : mine.mu;
         }
         finish_stats(mine, a, sh);
         const Divisor my_divisor = make_divisor(mine.denom, a.off);
-        if (a.stats && lane < kRows && row0 + lane < a.rows) {      // lane r holds the chain of row r
+        if (SAVE && lane < kRows && row0 + lane < a.rows) {         // lane r holds the chain of row r
             float4* out = reinterpret_cast<float4*>(a.stats + (row0 + lane) * kStatCount);
             out[0] = make_float4(mine.mu, mine.v, mine.e, my_divisor.flush_max);
             out[1] = make_float4(my_divisor.pass_max, i2f(my_divisor.sub), div_by(1.0f, my_divisor), mine.denom);
@@ -246,6 +246,7 @@ __host__ __device__ constexpr int rows_per_warp_bwd(int slots) { return slots <=
 // SAVED: the row scalars come from the forward pass (LnArgs::stats) instead of being recomputed from x:
 // no first two row sums and no forward scalar chain, so a warp no longer needs several rows in flight to
 // share that chain, needs fewer registers and more warps fit on an SM (approximate gradients only).
+// (Requesting the next rows from the L2 ahead of time measured 8 % slower here, as in the recomputing form.)
 #ifndef PAMK_LN_SAVED_ROWS
 #define PAMK_LN_SAVED_ROWS 2
 #endif
@@ -468,11 +469,11 @@ int launch(const LnArgs& a, int grid, cudaStream_t st) {
 #define PAMK_LN(V, N)                                                                   \
     do {                                                                                \
         if (a.width == 32 * (V) * (N)) {                                                \
-            if (BWD) ln_bwd_kernel<V, N, APPROX, true, SAVED><<<grid, kThreads, 0, st>>>(a); \
-            else ln_fwd_kernel<V, N, true><<<grid, kThreads, 0, st>>>(a);               \
+            if constexpr (BWD) ln_bwd_kernel<V, N, APPROX, true, SAVED><<<grid, kThreads, 0, st>>>(a); \
+            else ln_fwd_kernel<V, N, true, SAVED><<<grid, kThreads, 0, st>>>(a);        \
         } else {                                                                        \
-            if (BWD) ln_bwd_kernel<V, N, APPROX, false, SAVED><<<grid, kThreads, 0, st>>>(a); \
-            else ln_fwd_kernel<V, N, false><<<grid, kThreads, 0, st>>>(a);              \
+            if constexpr (BWD) ln_bwd_kernel<V, N, APPROX, false, SAVED><<<grid, kThreads, 0, st>>>(a); \
+            else ln_fwd_kernel<V, N, false, SAVED><<<grid, kThreads, 0, st>>>(a);       \
         }                                                                               \
         return check_launch();                                                          \
     } while (0)
@@ -516,7 +517,7 @@ int pamk_layer_norm_fwd_save(const float* x, const float* weight, const float* b
     if (rows == 0) return PAMK_OK;
     if (!x || !y || !stats || (reinterpret_cast<uintptr_t>(stats) & 15u)) return PAMK_ERR_ARG;
     LnArgs a{x, weight, bias, nullptr, y, nullptr, rows, (int)width, (float)width, eps, offset_bits(offset), stats};
-    return launch<false, false>(a, pick_grid(rows, false), static_cast<cudaStream_t>(stream));
+    return launch<false, false, true>(a, pick_grid(rows, false), static_cast<cudaStream_t>(stream));
 }
 
 int pamk_layer_norm_bwd_saved(const float* x, const float* weight, const float* dy, const float* stats, float* dx,
