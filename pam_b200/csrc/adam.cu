@@ -18,7 +18,7 @@
 namespace pamk {
 namespace {
 
-constexpr int kTensorsPerLaunch = 24;
+constexpr int kTensorsPerLaunch = 256;     // (an 11 KB kernel argument: within the 32 KB that sm_70 and later take)
 constexpr int kThreads = 256;
 constexpr int kPerBlock = kThreads * 4;
 
@@ -28,6 +28,10 @@ struct AdamTable {
     float* m[kTensorsPerLaunch];
     float* v[kTensorsPerLaunch];
     int64_t n[kTensorsPerLaunch];
+    // blocks [first[k], first[k + 1]) of the launch's one-dimensional grid belong to tensor k, so that a
+    // table that mixes an embedding matrix with bias vectors launches no block without work
+    unsigned first[kTensorsPerLaunch + 1];
+    int used;
 };
 
 struct AdamScalars {
@@ -50,9 +54,13 @@ __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, 
 }
 
 __global__ void __launch_bounds__(kThreads) adam_kernel(const AdamTable t, const AdamScalars s) {
-    const int which = blockIdx.y;
+    int which = 0, hi = t.used;                    // largest k with first[k] <= blockIdx.x (the same for the whole CTA)
+    while (hi - which > 1) {
+        const int mid = (which + hi) >> 1;
+        if (blockIdx.x >= t.first[mid]) which = mid; else hi = mid;
+    }
     const int64_t n = t.n[which];
-    const int64_t base = (int64_t)blockIdx.x * kPerBlock;
+    const int64_t base = (int64_t)(blockIdx.x - t.first[which]) * kPerBlock;
     if (base >= n) return;
     float* __restrict__ p = t.p[which];
     const float* __restrict__ g = t.g[which];
@@ -107,19 +115,25 @@ int pamk_adam_step(float* const* p, const float* const* g, float* const* m, floa
     for (int k = 0; k < count;) {
         AdamTable t{};
         int used = 0;
-        int64_t longest = 0;
+        int64_t blocks = 0;
         for (; k < count && used < kTensorsPerLaunch; ++k) {     // k carries on where the last table ended
             if (n[k] < 0) return PAMK_ERR_ARG;
             if (n[k] == 0) continue;
             if (!p[k] || !g[k] || !m[k] || !v[k]) return PAMK_ERR_ARG;
+            const int64_t mine = (n[k] + kPerBlock - 1) / kPerBlock;
+            if (blocks + mine > 0x7fffffff) {                    // this tensor starts the next table
+                if (used == 0) return PAMK_ERR_SIZE;
+                break;
+            }
             t.p[used] = p[k]; t.g[used] = g[k]; t.m[used] = m[k]; t.v[used] = v[k]; t.n[used] = n[k];
-            longest = n[k] > longest ? n[k] : longest;
+            t.first[used] = (unsigned)blocks;
+            blocks += mine;
             ++used;
         }
         if (used == 0) continue;
-        const int64_t blocks = (longest + kPerBlock - 1) / kPerBlock;
-        if (blocks > 0x7fffffff) return PAMK_ERR_SIZE;
-        adam_kernel<<<dim3((unsigned)blocks, (unsigned)used), kThreads, 0, st>>>(t, s);
+        t.first[used] = (unsigned)blocks;
+        t.used = used;
+        adam_kernel<<<(unsigned)blocks, kThreads, 0, st>>>(t, s);
         const int rc = check_launch();
         if (rc != PAMK_OK) return rc;
     }
