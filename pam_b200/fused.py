@@ -310,6 +310,88 @@ class _AttentionQKV(torch.autograd.Function):
         return dqkv, None, None, None
 
 
+def attention_heads_supported(q, k, v, num_heads, mask=None, approx_bwd=False):
+    """Like attention_supported, for separate query / key / value projections ([B, T, d], [B, S, d], [B, S, d])
+    and an optional additive mask that needs no gradient."""
+    for t in (q, k, v):
+        if not (enabled and isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.float32 and t.dim() == 3):
+            return False
+    if q.numel() == 0 or k.numel() == 0 or k.shape != v.shape or q.shape[0] != k.shape[0] or q.shape[2] != k.shape[2]:
+        return False
+    if q.shape[2] % num_heads or q.shape[0] * num_heads > 65535 or k.shape[1] > _MAX_ROW:
+        return False
+    if mask is not None and not (isinstance(mask, torch.Tensor) and mask.is_cuda and mask.dtype == torch.float32
+                                 and not mask.requires_grad):
+        return False
+    approx = (approx_bwd,) if isinstance(approx_bwd, bool) else tuple(approx_bwd)
+    return all(approx)
+
+
+class _AttentionHeads(torch.autograd.Function):
+    """softmax(q k^T + mask) v per head for separate projections q [B, T, d], k, v [B, S, d] (the explicit
+    branch of the fairseq fork's attention, fairseq/modules/multihead_attention.py:618-783, which splits the
+    heads into copies, multiplies, adds the mask, takes the softmax, multiplies and merges the heads through
+    another copy).  As in _AttentionQKV the heads are strided views of the projections, the context is written
+    token-major, every product has the shape and split-K plan of the chain's, and the values are the chain's
+    bit for bit."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, mask, heads, offset):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        B, T, d = q.shape
+        S = k.shape[1]
+        hd = d // heads
+        dev = q.device
+        scores = torch.empty(B * heads, T, S, dtype=torch.float32, device=dev)
+        _strided_product(dev, q.data_ptr(), k.data_ptr(), scores.data_ptr(), B, heads, T, S, hd,
+                         (T * d, hd, d, 1), (S * d, hd, 1, d), (heads * T * S, T * S, S), offset)
+        if mask is not None:
+            scores.add_(mask)
+        probs, expo = _softmax_forward_saving(scores.view(-1, S), offset)
+        out = torch.empty(B, T, d, dtype=torch.float32, device=dev)
+        _strided_product(dev, probs.data_ptr(), v.data_ptr(), out.data_ptr(), B, heads, T, hd, S,
+                         (heads * T * S, T * S, S, 1), (S * d, hd, d, 1), (T * d, hd, d), offset)
+        ctx.save_for_backward(q, k, v, expo, probs)
+        ctx.cfg = (heads, offset)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        q, k, v, expo, probs = ctx.saved_tensors
+        heads, offset = ctx.cfg
+        B, T, d = q.shape
+        S = k.shape[1]
+        hd = d // heads
+        dev = q.device
+        g = g.contiguous()
+        s_scores, s_q, s_kv = (heads * T * S, T * S, S, 1), (T * d, hd, d, 1), (S * d, hd, d, 1)
+        # d probs = d context v^T
+        dprobs = torch.empty(B * heads, T, S, dtype=torch.float32, device=dev)
+        _strided_product(dev, g.data_ptr(), v.data_ptr(), dprobs.data_ptr(), B, heads, T, S, hd,
+                         s_q, (S * d, hd, 1, d), (heads * T * S, T * S, S), offset)
+        # d v = probs^T d context
+        dv = torch.empty_like(v)
+        _strided_product(dev, probs.data_ptr(), g.data_ptr(), dv.data_ptr(), B, heads, S, hd, T,
+                         (heads * T * S, T * S, 1, S), s_q, (S * d, hd, d), offset)
+        # d scores (the mask is a constant)
+        dscores = _softmax_backward_saved(expo, dprobs.view(-1, S), offset)
+        # d q = d scores k
+        dq = torch.empty_like(q)
+        _strided_product(dev, dscores.data_ptr(), k.data_ptr(), dq.data_ptr(), B, heads, T, hd, S,
+                         s_scores, s_kv, (T * d, hd, d), offset)
+        # d (k^T) = q^T d scores as the chain computes it ([head_dim, S] per head), then transposed into d k
+        dkt = torch.empty(B, heads, hd, S, dtype=torch.float32, device=dev)
+        _strided_product(dev, q.data_ptr(), dscores.data_ptr(), dkt.data_ptr(), B, heads, hd, S, T,
+                         (T * d, hd, 1, d), s_scores, (heads * hd * S, hd * S, S), offset)
+        dk = torch.empty_like(k)
+        dk.view(B, S, heads, hd).copy_(dkt.permute(0, 3, 1, 2))
+        return dq, dk, dv, None, None, None
+
+
+def attention_heads(q, k, v, num_heads, mask=None, *, offset=None):
+    return _AttentionHeads.apply(q, k, v, mask, int(num_heads), _offset(offset))
+
+
 def attention_qkv(qkv, num_heads, scale, *, offset=None):
     return _AttentionQKV.apply(qkv, int(num_heads), float(scale), _offset(offset))
 

@@ -145,12 +145,17 @@ class MultiheadAttention(nn.Module):
         self.q_proj = linear_factory(embed_dim, embed_dim, bias=True)
         self.out_proj = linear_factory(embed_dim, embed_dim, bias=True)
         self.gain_op, self.bmm_op, self.softmax_op = op_dict["mul"], op_dict["bmm"], op_dict["softmax"]
+        self.ops = op_dict
 
     def forward(self, query, memory, attn_mask=None):
         B, T, d = query.shape
         S, H, hd = memory.shape[1], self.num_heads, self.head_dim
         q = self.gain_op(self.q_proj(query), self.scaling)
         k, v = self.k_proj(memory), self.v_proj(memory)
+        bound = _pam_binding(self.ops, ("bmm", "softmax"))
+        if bound is not None and fused.attention_heads_supported(q, k, v, H, attn_mask, bound.get("approx_bwd", False)):
+            # the same products, mask and softmax on strided views of the projections: no copies around them
+            return self.out_proj(fused.attention_heads(q, k, v, H, attn_mask, offset=bound.get("offset")))
         split = lambda t, L: t.reshape(B, L, H, hd).transpose(1, 2).reshape(B * H, L, hd)
         w = self.bmm_op(split(q, T), split(k, S).transpose(1, 2))
         if attn_mask is not None:

@@ -78,3 +78,40 @@ def test_unsupported_calls_are_refused():
     assert not fused.attention_supported(qkv, 4, (True, False))
     assert not fused.attention_supported(qkv, 5, True)              # 24 is not 3 * 5 * head_dim
     assert not fused.attention_supported(qkv.cpu(), 4, True)
+
+
+def heads_chain(ops, q, k, v, heads, mask, kw):
+    """The explicit branch of the fairseq fork's attention after the projections
+    (fairseq/modules/multihead_attention.py:618-783): heads split into copies, bmm, mask, softmax, bmm."""
+    B, T, d = q.shape
+    S, hd = k.shape[1], d // heads
+    split = lambda t, L: t.reshape(B, L, heads, hd).transpose(1, 2).reshape(B * heads, L, hd)
+    w = ops.bmm(split(q, T), split(k, S).transpose(1, 2), **kw)
+    if mask is not None:
+        w = w + mask
+    w = ops.softmax(w, dim=-1, **kw)
+    return ops.bmm(w, split(v, S), **kw).reshape(B, heads, T, hd).transpose(1, 2).reshape(B, T, d)
+
+
+@pytest.mark.parametrize("B,T,S,heads,hd,masked", [(128, 32, 32, 4, 128, True), (128, 32, 32, 4, 128, False), (3, 17, 29, 4, 16, False),
+                                                    (2, 40, 40, 8, 8, True), (5, 1, 7, 2, 4, False), (2, 200, 197, 3, 64, False)])
+@pytest.mark.parametrize("offset", [None, 1.0552])
+def test_strided_attention_over_separate_projections_equals_the_chain(B, T, S, heads, hd, masked, offset):
+    import pam_b200 as pam
+    from pam_b200 import fused
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(B * 100 + T + S)
+    d = heads * hd
+    q0, k0, v0 = (torch.randn(B, L, d, generator=g).to(dev) for L in (T, S, S))
+    dout = torch.randn(B, T, d, generator=g).to(dev)
+    mask = torch.triu(torch.full((T, S), float("-inf")), diagonal=1).to(dev) if masked else None
+    kw = dict(KW, offset=offset)
+    assert fused.attention_heads_supported(q0, k0, v0, heads, mask, True)
+    grads = []
+    for use_fused in (True, False):
+        q, k, v = (t.clone().requires_grad_() for t in (q0, k0, v0))
+        y = fused.attention_heads(q, k, v, heads, mask, offset=offset) if use_fused else heads_chain(pam, q, k, v, heads, mask, kw)
+        y.backward(dout)
+        grads.append((y.detach(), q.grad, k.grad, v.grad))
+    for name, a, b in zip(("context", "d q", "d k", "d v"), *grads):
+        assert_bits_equal(a, b, name)
