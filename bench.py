@@ -628,7 +628,7 @@ def training_step(args, case, rank, world, dev, steps, warmup):
     params = model
     leaves = list(model.parameters())
     opt = optim.Adam(leaves, opt_functional_cfg="pam", **hyper)
-    buckets = parallel.GradientBuckets(leaves)       # all-reduce per 25 MB bucket, overlapped with the backward pass
+    buckets = parallel.GradientBuckets(leaves)       # bucketed all-reduce, overlapped with the backward pass
     launches0 = None
     times, reduce_times, losses = [], [], []
     for it in range(warmup + steps):

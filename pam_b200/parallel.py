@@ -56,7 +56,8 @@ class GradientBuckets:
     """Data-parallel gradient sum overlapped with the backward pass.
 
     Parameters are grouped, in reverse order of registration (roughly the order in which their
-    gradients become ready), into buckets of about `bucket_bytes`.  A hook on each parameter fires
+    gradients become ready), into buckets of about `bucket_bytes` (default: 25 MB, or an eighth of all
+    gradients if that is less).  A hook on each parameter fires
     when its gradient has been accumulated; when the last gradient of a bucket arrives the bucket is
     flattened and its all-reduce is started asynchronously, so it travels over NVLink while the rest
     of the backward pass computes.  `finish()` waits for the reductions and copies the sums back into
@@ -67,10 +68,15 @@ class GradientBuckets:
         loss.backward(); buckets.finish()        # every step, before the optimizer
     """
 
-    def __init__(self, params, bucket_bytes=25 << 20, group=None, average=False):
+    def __init__(self, params, bucket_bytes=None, group=None, average=False):
         self.group, self.average = group, average
         self.active = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
         self.params = [p for p in params if p.requires_grad]
+        if bucket_bytes is None:
+            # 25 MB as DistributedDataParallel takes, but at least eight buckets, so that a model whose
+            # gradients fit one such bucket (DeiT-tiny: 23 MB) still overlaps its reduction with the backward pass
+            total = sum(p.numel() * p.element_size() for p in self.params)
+            bucket_bytes = min(25 << 20, max(1 << 20, total // 8))
         self.buckets, self.owner = [], {}
         current, size = [], 0
         for p in reversed(self.params):
