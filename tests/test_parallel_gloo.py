@@ -112,3 +112,18 @@ def test_shard_rows_edges():
     assert shard_rows(0, 0, 1) == (0, 0)
     with pytest.raises(ValueError):
         shard_rows(5, 2, 2)
+
+
+def test_gradient_buckets_default_size_overlaps_small_models():
+    """The default bucket size is 25 MB or an eighth of all gradients, whichever is less: a model whose
+    gradients would fit one 25 MB bucket still gets about eight reductions to overlap with its backward
+    pass (no process group is needed to look at the grouping)."""
+    import torch
+    from pam_b200 import parallel
+    small = [torch.nn.Parameter(torch.zeros(250_000)) for _ in range(23)]           # 23 MB of gradients
+    buckets = parallel.GradientBuckets(small)
+    assert 7 <= len(buckets.buckets) <= 12
+    assert sum(len(b) for b in buckets.buckets) == len(small)
+    large = [torch.nn.Parameter(torch.zeros(4_000_000)) for _ in range(40)]         # 640 MB: 25 MB buckets
+    assert len(parallel.GradientBuckets(large).buckets) >= 20
+    assert len(parallel.GradientBuckets(small, bucket_bytes=25 << 20).buckets) == 1
