@@ -607,7 +607,8 @@ bool vectorisable(const MatArg& m, bool kc, int rows, int K) {
 
 // ---- planning: tile shape and split-K ---------------------------------------------------------------
 // The kernel is issue-bound, so the time of a launch is (the largest number of tiles any SM ends up
-// with) x (work per tile), inflated when an SM holds too few warps to keep its schedulers busy.
+// with) x (work per tile), inflated when an SM holds too few warps to keep its schedulers busy,
+// which is also the state of the SMs that run the last, partly filled wave of a larger launch.
 enum TileKind { kTileLarge = 0, kTileSmall = 1, kTileTiny = 2 };
 
 struct Plan {
@@ -631,25 +632,38 @@ Plan plan_for(int mode, int64_t batch, int64_t M, int64_t N, int64_t K, int spli
         const int64_t chunk_slabs = (slabs + s - 1) / s;
         s = (slabs + chunk_slabs - 1) / chunk_slabs;         // drop ranges that would be empty
         *actual = s;
-        const int64_t per_sm = (tiles * s + sms - 1) / sms;
-        const double warps = (double)(per_sm < ctas_per_sm ? per_sm : ctas_per_sm) * (T::kThreads / 32);
         // measured: 16 resident warps per SM saturate the issue slots, 14 reach about 86 % of that,
         // 8 about 74 %
-        const double util = warps >= 16.0 ? 1.0 : (warps >= 8.0 ? 0.58 + 0.02 * warps : warps / 10.8);
+        auto util = [](int64_t ctas) {
+            const double warps = (double)ctas * (T::kThreads / 32);
+            return warps >= 16.0 ? 1.0 : (warps >= 8.0 ? 0.58 + 0.02 * warps : warps / 10.8);
+        };
         // the smaller the tile, the more bytes are staged (and fragments loaded) per MAC
         const double staging = T::BM >= 128 ? 1.0 : (T::BM >= 64 ? 1.06 : 1.25);
         // every CTA also pays a prologue (first loads exposed) and an epilogue worth about 16 k-steps
-        const double per_cta = (double)(chunk_slabs * T::BK) + 16.0;
-        return (double)per_sm * T::BM * T::BN * per_cta / util * staging +
-               (s > 1 ? 1.1e6 : 0.0);                         // the reduction pass and its launch (~12 us)
+        const double per_cta = (double)T::BM * T::BN * ((double)(chunk_slabs * T::BK) + 16.0);
+        const int64_t ctas = tiles * s;
+        // CTAs spread evenly over the SMs ...
+        const int64_t per_sm = (ctas + sms - 1) / sms;
+        double cost = (double)per_sm * per_cta / util(per_sm < ctas_per_sm ? per_sm : ctas_per_sm);
+        // ... and CTAs that run as full waves over all slots plus a last, partly filled one whose SMs
+        // hold few warps.  The hardware refills slots one by one, which lies between the two: a sweep
+        // of tile x split over products of 1 to 9 waves fits 0.62 / 0.38 (a vocabulary-sized weight
+        // gradient of 1.07 waves loses 24 % to its tail without a split).
+        const int64_t full = ctas / slots, rest = (ctas - full * slots + sms - 1) / sms;
+        if (full >= 1) {
+            const double waves = (double)(full * ctas_per_sm) * per_cta + (rest ? (double)rest * per_cta / util(rest) : 0.0);
+            cost = 0.62 * cost + 0.38 * waves;
+        }
+        return cost * staging + (s > 1 ? 1.1e6 : 0.0);        // the reduction pass and its launch (~12 us)
     };
     Plan pl;
     pl.tile = T::BM >= 128 ? kTileLarge : (T::BM >= 64 ? kTileSmall : kTileTiny);
     int64_t s = split_request > 0 ? split_request : 1, actual = 1;
     pl.cost = cost_of(s, &actual);
     pl.splits = (int)actual;
-    if (split_request == 0 && tiles < 2 * slots && slabs >= 8) {  // automatic: try to fill the SMs
-        int64_t limit = 2 * slots / tiles;                   // up to two full waves of CTAs
+    if (split_request == 0 && tiles < 8 * slots && slabs >= 8) {  // automatic: fill the SMs, shorten the tail
+        int64_t limit = 8 * slots / tiles;                   // up to eight full waves of CTAs
         if (limit < 2) limit = 2;
         if (limit > slabs / 4) limit = slabs / 4;            // keep at least four slabs per range
         if (limit > 64) limit = 64;

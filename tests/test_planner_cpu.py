@@ -24,6 +24,16 @@ def test_deit_products_keep_their_measured_best_split(lib, M, N, K, split):
     assert lib.pamk_matmul_auto_split(1, M, N, K) == split
 
 
+@pytest.mark.parametrize("M,N,K,split", [
+    (10000, 512, 4096, 6),     # 316 tiles of 128 x 128 on 296 slots: 1.07 waves unsplit (measured 1.88 -> 1.52 ms)
+    (4096, 512, 10000, 8),     # the input gradient of the same projection (1.58 -> 1.51 ms)
+    (2048, 3072, 2048, 3),     # 384 tiles: 1.3 waves unsplit (1.11 -> 0.97 ms)
+    (4096, 10000, 512, 1),     # 8.5 waves: nothing to gain
+])
+def test_products_of_one_to_two_waves_are_split_to_shorten_the_last_wave(lib, M, N, K, split):
+    assert lib.pamk_matmul_auto_split(1, M, N, K) == split
+
+
 def test_planner_basic_properties(lib):
     # large outputs fill the GPU without a split; tiny K is never split; empty problems do not divide by zero
     assert lib.pamk_matmul_auto_split(1, 4096, 4096, 4096) == 1
