@@ -652,7 +652,7 @@ Plan plan_for(int mode, int64_t batch, int64_t M, int64_t N, int64_t K, int spli
         // gradient of 1.07 waves loses 24 % to its tail without a split).
         const int64_t full = ctas / slots, rest = (ctas - full * slots + sms - 1) / sms;
         if (full >= 1) {
-            const double waves = (double)(full * ctas_per_sm) * per_cta + (rest ? (double)rest * per_cta / util(rest) : 0.0);
+            const double waves = (double)(full * ctas_per_sm) * per_cta / util(ctas_per_sm) + (rest ? (double)rest * per_cta / util(rest) : 0.0);
             cost = 0.62 * cost + 0.38 * waves;
         }
         return cost * staging + (s > 1 ? 1.1e6 : 0.0);        // the reduction pass and its launch (~12 us)
