@@ -691,16 +691,18 @@ Plan make_plan(int mode, int64_t batch, int64_t M, int64_t N, int64_t K, int spl
     const Plan small = plan_for<TileSmall>(mode, batch, M, N, K, split_request);
     if (g_tile_policy == 2 || (g_tile_policy == 3 && mode != kPam)) return small;
     Plan best = small.cost < large.cost ? small : large;
-    // The 32x32 tile is considered where at least half of every 64x64 tile would be empty, and where the
-    // launch is large enough (two waves of 64x64 tiles) that only throughput counts and the model's
-    // comparison is padding against staging: 192 x 197x197x64 pads to 256x256 with the 64x64 tile, to
-    // 224x224 with this one (measured on 120 such products: median -12 %, worst +6 %).  Elsewhere it is
-    // slower per product than the cost model's occupancy term suggests.
-    const int64_t small_tiles = batch * ((M + TileSmall::BM - 1) / TileSmall::BM) * ((N + TileSmall::BN - 1) / TileSmall::BN);
-    const bool throughput_bound = small_tiles >= 2 * (int64_t)sm_count() * TileSmall::kCtasPerSm;
-    if (mode == kPam && (g_tile_policy == 3 || M <= TileTiny::BM || N <= TileTiny::BN || throughput_bound)) {
+    // The 32x32 tile wins where the 64x64 tile pads much (192 x 197x197x64: 256x256 against 224x224
+    // outputs) or leaves most SMs empty.  Its modelled cost has to be lower by a margin that sweeps of
+    // tile x split fitted: 10 % for launches of at least two waves of 64x64 tiles, where only throughput
+    // counts (120 products: median -12 %, worst +6 %), and for matrices no larger than one tile in a
+    // dimension; 20 % for smaller launches, where the model overrates the tile (106 products with that
+    // margin: median -22 %, one slower, by 0.3 %; of 34 with 10 to 20 %, 13 were slower).
+    if (mode == kPam) {
+        const int64_t small_tiles = batch * ((M + TileSmall::BM - 1) / TileSmall::BM) * ((N + TileSmall::BN - 1) / TileSmall::BN);
+        const bool throughput_bound = small_tiles >= 2 * (int64_t)sm_count() * TileSmall::kCtasPerSm;
+        const double margin = throughput_bound || M <= TileTiny::BM || N <= TileTiny::BN ? 0.9 : 0.8;
         const Plan tiny = plan_for<TileTiny>(mode, batch, M, N, K, split_request);
-        if (g_tile_policy == 3 || tiny.cost < 0.9 * best.cost) best = tiny;
+        if (g_tile_policy == 3 || tiny.cost < margin * best.cost) best = tiny;
     }
     return best;
 }
