@@ -3,6 +3,8 @@
 #ifndef PAM_B200_TESTING_H
 #define PAM_B200_TESTING_H
 
+#include <stdint.h>
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -14,6 +16,11 @@ extern "C" {
  * 32x32 (products that have no 32x32 kernel use 64x64).  Process-wide and not thread-safe, which is
  * why it is kept out of pam_b200.h.  No counterpart in the reference. */
 int pamk_test_set_tile_policy(int policy);
+
+/* The tile edge (128, 64 or 32) the cost model gives the PAM product of these dimensions under the
+ * current policy, with the automatic split: lets a test pin the measured-best choices without a GPU.
+ * Negative (PAMK_ERR_ARG) for an empty problem.  No counterpart in the reference. */
+int pamk_test_planned_tile(int64_t batch, int64_t M, int64_t N, int64_t K);
 
 #ifdef __cplusplus
 }

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "pamk_matmul_workspace_bytes": (_sz, [_i64, _i64, _i64, _i]),
     "pamk_matmul_auto_split": (_i, [_i64] * 4),
     "pamk_test_set_tile_policy": (_i, [_i]),
+    "pamk_test_planned_tile": (_i, [_i64] * 4),
     "pamk_matmul_static_scratch_bytes": (_sz, []),
     "pamk_matmul_static_scratch": (_i, [_p, _p, _p] + [_i64] * 10 + [_f, _i, _p]),
     "pamk_matmul_bwd": (_i, [_p] * 4 + [_i64] * 13 + [_i, _f, _i, _p, ctypes.c_size_t, _p]),

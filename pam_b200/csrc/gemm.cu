@@ -850,6 +850,12 @@ int pamk_test_set_tile_policy(int policy) {
     return PAMK_OK;
 }
 
+int pamk_test_planned_tile(int64_t batch, int64_t M, int64_t N, int64_t K) {
+    if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return PAMK_ERR_ARG;
+    const int tile = make_plan(kPam, batch, M, N, K, 0).tile;
+    return tile == kTileLarge ? 128 : (tile == kTileSmall ? 64 : 32);
+}
+
 int pamk_matmul_auto_split(int64_t batch, int64_t M, int64_t N, int64_t K) {
     if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 1;
     return make_plan(kPam, batch, M, N, K, 0).splits;

@@ -34,6 +34,19 @@ def test_products_of_one_to_two_waves_are_split_to_shorten_the_last_wave(lib, M,
     assert lib.pamk_matmul_auto_split(1, M, N, K) == split
 
 
+@pytest.mark.parametrize("batch,M,N,K,tile", [
+    (1, 16384, 16384, 16384, 128), (1, 4096, 4096, 4096, 128),   # large squares
+    (1, 4096, 512, 512, 128), (1, 10000, 512, 4096, 128),        # transformer products: large tile, K ranges
+    (1, TOKENS, 192, 192, 64), (1, TOKENS, 576, 192, 64),        # DeiT-tiny layers: 197 x 3 tiles of 64 fill the SMs
+    (192, 197, 197, 64, 32),                                     # its score products: 224 x 224 instead of 256 x 256 padded
+    (512, 32, 32, 128, 32),                                      # attention over 32 tokens
+    (8, 160, 197, 64, 32),                                       # a launch that leaves most SMs empty (21.6 -> 9.4 us)
+])
+def test_tile_choices_that_sweeps_measured_best(lib, batch, M, N, K, tile):
+    assert lib.pamk_test_set_tile_policy(0) == 0
+    assert lib.pamk_test_planned_tile(batch, M, N, K) == tile
+
+
 def test_planner_basic_properties(lib):
     # large outputs fill the GPU without a split; tiny K is never split; empty problems do not divide by zero
     assert lib.pamk_matmul_auto_split(1, 4096, 4096, 4096) == 1
